@@ -10,7 +10,9 @@ batch.rs:209-212) or is cut back (``truncate``, batch.rs:220-227), and reused at
 Beyond the reference:
   * layers are sorted into GROUPS by what they need (key/value heads, head size, window); each
     group has a page pool, a device tensor and block tables of its own, so a group that keeps a
-    window of keys gives pages back as the window passes them while another keeps all keys;
+    window of keys gives pages back as the window passes them while another keeps all keys; a
+    window may keep a request's first positions readable behind it (``KVCacheSpec.keep_first``):
+    the pages that hold them stay with the request until it ends;
   * a step's allocation is all-or-nothing (the reference leaves a partial allocation behind
     when the pool runs out, batch.rs:243-254);
   * every request owns one STATE SLOT: an index into per-slot tensors of fixed size (a mixer's
@@ -262,6 +264,10 @@ class CacheManager:
             return 0
         return max(0, pos0 - g.spec.window + 1) // self.page_size
 
+    def _first_kept_blocks(self, g: CacheGroup) -> int:
+        """How many logical blocks at the start of a request hold positions that stay readable behind the window."""
+        return -(-g.spec.keep_first // self.page_size) if g.spec.keep_first > 0 else 0
+
     def pages_needed(self, req: RequestCache, n_new: int) -> List[int]:
         """Pages per group that appending ``n_new`` tokens would take from the pool."""
         self._require_live(req)
@@ -307,7 +313,7 @@ class CacheManager:
         for g, blocks, row in zip(self.groups, req.blocks, req.table_rows):
             if g.spec.window > 0:
                 first = self._first_needed_block(g, req.n_tokens)  # the next query stands at n_tokens
-                for b in range(min(first, len(blocks))):
+                for b in range(self._first_kept_blocks(g), min(first, len(blocks))):
                     if blocks[b] >= 0:
                         g.pool.give_back(blocks[b])
                         blocks[b] = -1
@@ -330,7 +336,8 @@ class CacheManager:
         for g, blocks, row in zip(self.groups, req.blocks, req.table_rows):
             if g.spec.window > 0 and n_tokens < req.n_tokens:
                 first = self._first_needed_block(g, n_tokens)
-                if any(blocks[b] < 0 for b in range(first, min(keep, len(blocks)))):
+                kept = range(min(self._first_kept_blocks(g), keep, len(blocks)))
+                if any(blocks[b] < 0 for b in [*kept, *range(first, min(keep, len(blocks)))]):
                     raise CacheError("truncate: pages behind the window were already given back")
             while len(blocks) > keep:
                 p = blocks.pop()

@@ -14,6 +14,21 @@
 #define NIB_STATUS_BAD_PAGE 1
 #define NIB_STATUS_WAIT_TIMEOUT 2
 
+// Options of the attention kernels that take them, on the scores and on the output:
+//   softcap > 0:  s <- softcap tanh(s / softcap) after the scale;
+//   slopes:       one number per query head, s <- s - slopes[h] (query position - key position);
+//   keep_first:   with a window, keys 0 .. keep_first - 1 stay visible behind it;
+//   gate:         head h's output of row t is multiplied by sigmoid(gate[t * ldg + h]);
+//   out_scale:    and by this constant.
+struct AttnExtras {
+  float softcap;
+  int keep_first;
+  const float* slopes;
+  const float* gate;
+  int ldg;
+  float out_scale;
+};
+
 #ifdef __cplusplus
 extern "C" {
 #endif
@@ -87,7 +102,8 @@ int nib_linear_skinny(int out_dtype, const void* a, int lda, const void* w, int 
 int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, void* out, int ldo,
                        const int* block_table, int max_blocks, const int* rows, const int* row_entry,
                        const int* positions, int T, int n_head, int n_kv_head, int head_dim,
-                       int page_size, int n_pages, float scale, int window, int sink, int* status,
+                       int page_size, int n_pages, float scale, int window, int sink, float softcap,
+                       int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int* status,
                        cudaStream_t stream);
 
 // tcgen05 attention for prompt portions (bfloat16, head size 64, page size a multiple of 16): tiles of
@@ -104,7 +120,8 @@ long long nib_attention_decode_scratch(int n_rows, int n_head, int head_dim, int
 int nib_attention_decode(int dtype, const void* q, int ldq, const void* cache, float* scratch, void* out,
                          int ldo, const int* block_table, int max_blocks, const int* rows,
                          const int* row_entry, const int* positions, int n_rows, int n_head, int n_kv_head,
-                         int head_dim, int page_size, int n_pages, float scale, int window, int sink, int chunk,
+                         int head_dim, int page_size, int n_pages, float scale, int window, int sink, float softcap,
+                         int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int chunk,
                          int n_splits, int* counters, int* status, cudaStream_t stream);
 
 // Tiled tensor-core attention for prompt portions (bfloat16, head sizes 16..128 in steps of 16).
@@ -216,6 +233,39 @@ int nib_moe_scale(int dtype, void* inner, const int* ids, const float* weights, 
 int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src, const void* w, const int* ids,
                     const float* weights, void* out, float* x, int T, int top, int n_expert, int N, int K, int act,
                     cudaStream_t stream);
+
+// Sinusoidal positions added to the 32-bit stream x [T, C]: entry 2i += sin(position * freqs[i]), entry 2i + 1 += cos.
+int nib_add_sinusoid(float* x, const int* positions, const double* freqs, int T, int C, cudaStream_t stream);
+
+// out[t, d] = act(pre[t, d]) * table[token_t, off + d] for d < D (tokens as in nib_embed).
+int nib_gate_by_table(int dtype, const float* pre, int ld, const int* tokens, const int* feedback, const void* table,
+                      int table_ld, int off, int D, int act, void* out, int ldo, int n_rows, cudaStream_t stream);
+
+// nib_rope_append with an RMS norm of every query and key head ahead of the rotation (weights of `dim` values shared
+// by the heads; either may be null).
+int nib_norm_rope_append(int dtype, const float* proj, int ld, int q_off, int k_off, int v_off, int n_head,
+                         int n_kv_head, int dim, int vdim, int hd, const float* wq, const float* wk, float eps,
+                         int rot_dims, const double* freqs, const int* positions, const int* row_entry, void* q_out,
+                         int ldq, void* cache, const int* block_table, int max_blocks, int page_size, int n_pages, int T,
+                         int* status, cudaStream_t stream);
+
+// Recurrent mixers with a matrix state per head (gated_scan.cu): the short causal convolution with its state, the
+// decays and strengths (and unit queries and keys) of the rows, the recurrence itself, and the gated norm behind it.
+int nib_short_conv(const float* proj, int ld, int c_off, int Cn, int taps, const float* w, const float* bias,
+                   float* state, long long state_stride, const int* row_entry, const int* entry_start,
+                   const int* entry_slot, float* out, int ldo, int T, int n_entries, int act, int fused,
+                   cudaStream_t stream);
+int nib_scan_prepare(const float* proj, int ld, int a_off, int w_off, const float* A_log, const float* dt_bias,
+                     float* cv, int ldc, int q_off, int k_off, int N, int n_head, int n_kq, int delta, float* coef, int T,
+                     cudaStream_t stream);
+int nib_gated_scan_padded(int N);
+int nib_gated_scan(int delta, const float* cv, int ldc, int q_off, int k_off, int v_off, int N, int V, int n_head,
+                   int kq_ratio, const float* coef, const float* skip, float* state, long long state_stride,
+                   long long s_off, const int* entry_start, const int* entry_slot, int n_entries, float* out, int ldo,
+                   cudaStream_t stream);
+int nib_gated_norm(int out_dtype, const float* o, int ldo, const float* gate, int ldg, const float* weight, int wlen,
+                   int n_groups, int gs, float eps, int gate_first, float out_scale, void* out, int ld_out, int T,
+                   cudaStream_t stream);
 
 #ifdef __cplusplus
 }

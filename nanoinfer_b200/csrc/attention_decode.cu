@@ -9,6 +9,8 @@
 // a small batch still fills the GPU.  Scores are (q . k) * scale for the keys lo..pos, in 32-bit
 // (crates/core/src/kernels/reference.rs:109-142).
 //
+// Options (AttnExtras, api.h): a soft cap and a distance bias on the scores, the first keys kept behind a window
+// (the first split walks them ahead of its own share), a per-head sigmoid gate and a constant on the output.
 #include "api.h"
 #include "common.cuh"
 
@@ -70,7 +72,7 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
                         const int* __restrict__ block_table, int max_blocks, const int* __restrict__ rows,
                         const int* __restrict__ row_entry, const int* __restrict__ positions, int n_head,
                         int n_kv_head, int head_dim, int page_size, int n_pages, float scale, int window,
-                        int sink, int chunk, int n_splits, int* counters, int* status,
+                        int sink, AttnExtras ex, int chunk, int n_splits, int* counters, int* status,
                         int cluster_merge) {
   constexpr int VN = Piece<T>::N;
   constexpr int BATCH = LPR / 2 < 4 ? LPR / 2 : 4;   // keys per lane group and batch
@@ -108,7 +110,16 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
   // batches of BK consecutive keys (BK divides 16, so a batch lies in one page); this warp's batches
   // are first_batch + warp + i * DEC_WARPS
   const int first_batch = empty ? 0 : k_begin / BK, last_batch = empty ? -1 : (k_end - 1) / BK;
-  const int n_mine = (first_batch + warp <= last_batch) ? (last_batch - first_batch - warp) / DEC_WARPS + 1 : 0;
+  const int n_main = (first_batch + warp <= last_batch) ? (last_batch - first_batch - warp) / DEC_WARPS + 1 : 0;
+  // keys 0 .. kept - 1 that the window has passed stay visible: the first split walks them, in batches of their
+  // own, ahead of its share of the window
+  const int kept = split == 0 ? min(ex.keep_first, lo) : 0;
+  const int last_kept = kept > 0 ? (kept - 1) / BK : -1;
+  const int n_kept = warp <= last_kept ? (last_kept - warp) / DEC_WARPS + 1 : 0;
+  const int n_mine = n_kept + n_main;
+  const float slope = ex.slopes ? ex.slopes[h] : 0.0f;
+  const bool plain_scores = !(ex.softcap > 0.0f) && slope == 0.0f;
+  int cur_j0 = 0;      // first key of the batch in kp/vp
   Piece<T> kp[BATCH], vp[BATCH];
   uint32_t live = 0;   // bit i: key i of the batch in kp/vp is one of this split's
   // where this lane's piece of a row lies: ((page * 2 + K|V) * n_kv_head + head) * page_size + slot) * head_dim + piece
@@ -116,7 +127,10 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
   const T* lane_base = cache + ((size_t)hk * page_size + group) * head_dim + c * VN;
   // asks for this lane's pieces of the warp's batch i
   auto fetch = [&](int i) {
-    const int j0 = (first_batch + warp + i * DEC_WARPS) * BK;
+    const bool in_kept = i < n_kept;
+    const int j0 = in_kept ? (warp + i * DEC_WARPS) * BK : (first_batch + warp + (i - n_kept) * DEC_WARPS) * BK;
+    const int j_lo = in_kept ? 0 : k_begin, j_hi = in_kept ? kept : k_end;
+    cur_j0 = j0;
     const int page = table[page_size == 16 ? (j0 >> 4) : j0 / page_size];
     live = 0;
     if (page < 0 || page >= n_pages) {
@@ -128,7 +142,7 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
 #pragma unroll
     for (int b = 0; b < BATCH; ++b) {
       const int j = j0 + b * GROUPS + group;
-      if (j >= k_begin && j < k_end) {
+      if (j >= j_lo && j < j_hi) {
         live |= 1u << b;
         if (has_piece) {
           kp[b].load(kr + b * GROUPS * head_dim);
@@ -138,7 +152,7 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
     }
   };
   // none of the first batch's keys is the one that the kernel ahead writes
-  const bool early = n_mine > 0 && (first_batch + warp) * BK + BK - 1 < pos;
+  const bool early = n_kept > 0 || (n_main > 0 && (first_batch + warp) * BK + BK - 1 < pos);
   if (early) fetch(0);
   pdl_wait();
   if (cluster_merge) cluster_wait();   // every block of the cluster runs by now
@@ -186,7 +200,14 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
       }
 #pragma unroll
       for (int d = 1; d < LPR; d <<= 1) dot += __shfl_xor_sync(0xffffffffu, dot, d);   // the group's lanes, in a fixed order
-      sc[b] = ((live >> b) & 1u) ? dot * scale2 : -INFINITY;
+      if (plain_scores) {
+        sc[b] = ((live >> b) & 1u) ? dot * scale2 : -INFINITY;
+      } else {
+        float sv = dot * scale;
+        if (ex.softcap > 0.0f) sv = ex.softcap * tanhf(sv / ex.softcap);
+        sv -= slope * (float)(pos - (cur_j0 + b * GROUPS + group));
+        sc[b] = ((live >> b) & 1u) ? sv * 1.4426950408889634f : -INFINITY;
+      }
     }
     float m_new = m;
 #pragma unroll
@@ -228,11 +249,12 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
   // a sink (one more term in the denominator: a key of score 0 without a value) counts once, where the row's
   // weights are divided
   const float L1 = (sink && n_splits == 1) ? L + pow2<T>(-M) : L;
+  const float mul1 = n_splits == 1 ? ex.out_scale * (ex.gate ? 1.0f / (1.0f + expf(-ex.gate[(size_t)t * ex.ldg + h])) : 1.0f) : 1.0f;
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
     for (int w = 0; w < ALL_GROUPS; ++w) acc += (gm[w] == -INFINITY) ? 0.0f : go[w * head_dim + d] * pow2<T>(gm[w] - M);
     if (n_splits == 1)
-      out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / L1);
+      out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / L1 * mul1);
     else if (cluster_merge)
       store_to_rank(xo + split * head_dim + d, 0, acc);
     else
@@ -279,13 +301,14 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
     if (ls > 0.0f) Lx += ls * pow2<T>(part_ml[2 * (base + sp)] - Mx);
   }
   if (sink) Lx += pow2<T>(-Mx);
+  const float mulx = ex.out_scale * (ex.gate ? 1.0f / (1.0f + expf(-ex.gate[(size_t)t * ex.ldg + h])) : 1.0f);
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
     for (int sp = 0; sp < n_splits; ++sp) {
       const float ls = part_ml[2 * (base + sp) + 1];
       if (ls > 0.0f) acc += part_o[(base + sp) * head_dim + d] * pow2<T>(part_ml[2 * (base + sp)] - Mx);
     }
-    out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / Lx);
+    out[(size_t)t * ldo + h * head_dim + d] = from_float<T>(acc / Lx * mulx);
   }
 }
 
@@ -293,8 +316,8 @@ template <typename T>
 static int launch_decode(const void* q, int ldq, const void* cache, float* part_o, float* part_ml, void* out,
                          int ldo, const int* block_table, int max_blocks, const int* rows, const int* row_entry,
                          const int* positions, int n_rows, int n_head, int n_kv_head, int head_dim,
-                         int page_size, int n_pages, float scale, int window, int sink, int chunk, int n_splits,
-                         int* counters, int* status, cudaStream_t stream) {
+                         int page_size, int n_pages, float scale, int window, int sink, AttnExtras ex, int chunk,
+                         int n_splits, int* counters, int* status, cudaStream_t stream) {
   dim3 grid(n_splits, n_head, n_rows);
   const int n_pieces = head_dim / Piece<T>::N;
   // two or four splits run as one cluster and merge through distributed shared memory (clusters of
@@ -304,7 +327,7 @@ static int launch_decode(const void* q, int ldq, const void* cache, float* part_
   launch_pdl_cluster(attention_decode_kernel<T, LPR>, dim3(grid), dim3(DEC_WARPS * 32),                            \
              (size_t)(DEC_WARPS * (32 / LPR) * (head_dim + 2) + n_splits * (head_dim + 2)) * sizeof(float), stream, \
              cluster, (const T*)q, ldq, (const T*)cache, part_o, part_ml, (T*)out, ldo, block_table, max_blocks,   \
-             rows, row_entry, positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, sink,     \
+             rows, row_entry, positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, sink, ex, \
              chunk, n_splits, counters, status, cluster > 1 ? 1 : 0)
   if (n_pieces <= 2) NIB_DECODE_LAUNCH(2);
   else if (n_pieces <= 4) NIB_DECODE_LAUNCH(4);
@@ -333,9 +356,11 @@ extern "C" int nib_attention_decode(int dtype, const void* q, int ldq, const voi
                                     void* out, int ldo, const int* block_table, int max_blocks, const int* rows,
                                     const int* row_entry, const int* positions, int n_rows, int n_head,
                                     int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
-                                    int window, int sink, int chunk, int n_splits, int* counters, int* status,
-                                    cudaStream_t stream) {
+                                    int window, int sink, float softcap, int keep_first, const float* slopes,
+                                    const float* gate, int ldg, float out_scale, int chunk, int n_splits,
+                                    int* counters, int* status, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
+  const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale};
   if (head_dim <= 0 || head_dim > DEC_MAX_HD || (head_dim & 7)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (page_size % 16 != 0 || chunk <= 0 || chunk % 16 != 0 || n_splits <= 0) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
@@ -346,11 +371,11 @@ extern "C" int nib_attention_decode(int dtype, const void* q, int ldq, const voi
   if (dtype == DT_F32)
     return launch_decode<float>(q, ldq, cache, part_o, part_ml, out, ldo, block_table, max_blocks, rows, row_entry,
                                 positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
-                                sink, chunk, n_splits, counters, status, stream);
+                                sink, ex, chunk, n_splits, counters, status, stream);
   if (dtype == DT_BF16)
     return launch_decode<bf16>(q, ldq, cache, part_o, part_ml, out, ldo, block_table, max_blocks, rows, row_entry,
                                positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
-                               sink, chunk, n_splits, counters, status, stream);
+                               sink, ex, chunk, n_splits, counters, status, stream);
   return NIB_ERR_BAD_ARGUMENT;
 }
 
@@ -411,5 +436,5 @@ extern "C" int nib_attention_decode_static(int dtype, const void* q, int ldq, co
   if (e != cudaSuccess) return (int)e;
   return nib_attention_decode(dtype, q, ldq, cache, scratch, out, ldo, block_table, max_blocks, rows, row_entry,
                               positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
-                              0, chunk, n_splits, counters, status, stream);
+                              0, 0.0f, 0, nullptr, nullptr, 0, 1.0f, chunk, n_splits, counters, status, stream);
 }

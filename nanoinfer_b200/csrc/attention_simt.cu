@@ -8,6 +8,10 @@
 // crates/metal/src/shaders/batch.metal:349-424), all in 32-bit.  A row's result depends on
 // its own keys only, never on what else the batch holds.  With `sink` the softmax's denominator has one
 // more term, exp(0): a key of score 0 that has no value, so that a row may attend to nothing.
+//
+// Options on the scores and the output (AttnExtras, api.h): a soft cap s <- cap tanh(s / cap); a distance
+// bias s <- s - slope_h (pos - j); with a window, the first `keep_first` keys stay visible behind it (at their
+// true positions); head h's output times sigmoid(gate[t, h]) and times one constant.
 #include "api.h"
 #include "common.cuh"
 
@@ -22,7 +26,8 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
                       T* out, int ldo, const int* __restrict__ block_table,
                       int max_blocks, const int* __restrict__ rows, const int* __restrict__ row_entry,
                       const int* __restrict__ positions, int n_head, int n_kv_head, int head_dim,
-                      int page_size, int n_pages, float scale, int window, int sink, int* __restrict__ status) {
+                      int page_size, int n_pages, float scale, int window, int sink, AttnExtras ex,
+                      int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   extern __shared__ float smem[];
@@ -47,10 +52,15 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
 #pragma unroll
   for (int i = 0; i < ATT_MAX_ND; ++i) o[i] = 0.0f;
   float m = -INFINITY, l = 0.0f;
+  const float slope = ex.slopes ? ex.slopes[h] : 0.0f;
+  // two runs of keys: those the window has passed but that are kept (0 .. keep_first - 1), then the window's
+  const int kept = min(ex.keep_first, lo);
 
-  for (int j0 = lo; j0 <= pos; j0 += 32) {
+  for (int run = kept > 0 ? 0 : 1; run < 2; ++run) {
+  const int j_begin = run == 0 ? 0 : lo, j_end = run == 0 ? kept : pos + 1;
+  for (int j0 = j_begin; j0 < j_end; j0 += 32) {
     const int j = j0 + lane;
-    const bool valid = j <= pos;
+    const bool valid = j < j_end;
     float s = -INFINITY;
     unsigned long long vo = 0;
     if (valid) {
@@ -64,6 +74,8 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
         float dot = 0.0f;
         for (int d = 0; d < head_dim; ++d) dot = fmaf(qs[d], to_float(kr[d]), dot);
         s = dot * scale;
+        if (ex.softcap > 0.0f) s = ex.softcap * tanhf(s / ex.softcap);
+        s -= slope * (float)(pos - j);
       }
     }
     const float m_new = fmaxf(m, warp_max(s));
@@ -75,7 +87,7 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
     pj[lane] = p;
     voff[lane] = vo;
     __syncwarp();
-    const int n_valid = min(32, pos - j0 + 1);
+    const int n_valid = min(32, j_end - j0);
     for (int jj = 0; jj < n_valid; ++jj) {
       const float pv = pj[jj];
       const T* vr = cache + voff[jj];
@@ -88,9 +100,11 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
     __syncwarp();
     m = m_new;
   }
+  }
   // a sink: one more term in the denominator, a key of score 0 that has no value
   if (sink) l += expf(-m);
-  const float inv = 1.0f / l;
+  float inv = ex.out_scale / l;
+  if (ex.gate) inv *= 1.0f / (1.0f + expf(-ex.gate[(size_t)t * ex.ldg + h]));
 #pragma unroll
   for (int i = 0; i < ATT_MAX_ND; ++i) {
     const int d = lane + 32 * i;
@@ -106,8 +120,11 @@ extern "C" int nib_attention_simt(int dtype, const void* q, int ldq, const void*
                                   int ldo, const int* block_table, int max_blocks, const int* rows,
                                   const int* row_entry, const int* positions, int T, int n_head,
                                   int n_kv_head, int head_dim, int page_size, int n_pages,
-                                  float scale, int window, int sink, int* status, cudaStream_t stream) {
+                                  float scale, int window, int sink, float softcap, int keep_first,
+                                  const float* slopes, const float* gate, int ldg, float out_scale, int* status,
+                                  cudaStream_t stream) {
   if (T <= 0) return 0;
+  const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale};
   if (head_dim <= 0 || head_dim > 32 * ATT_MAX_ND || (head_dim & 1)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
   if (T > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
@@ -116,11 +133,11 @@ extern "C" int nib_attention_simt(int dtype, const void* q, int ldq, const void*
   if (dtype == DT_F32)
     launch_pdl(attention_simt_kernel<float>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const float*)q, ldq, (const float*)cache, (float*)out, ldo, block_table, max_blocks, rows, row_entry,
-        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, sink, status);
+        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, sink, ex, status);
   else if (dtype == DT_BF16)
     launch_pdl(attention_simt_kernel<bf16>, dim3(grid), dim3(ATT_WARPS * 32), smem, stream, 
         (const bf16*)q, ldq, (const bf16*)cache, (bf16*)out, ldo, block_table, max_blocks, rows, row_entry,
-        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, sink, status);
+        positions, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window, sink, ex, status);
   else
     return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();

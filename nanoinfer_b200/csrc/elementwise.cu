@@ -32,6 +32,41 @@ __global__ void embed_kernel(const int* __restrict__ tokens, const int* __restri
   }
 }
 
+// Sinusoidal positions added to the stream: entry 2i of row t gets sin(pos_t * freqs[i]), entry 2i + 1 the cosine of
+// the same angle.  The frequencies come from the host in double precision; angle, sine and cosine are made in double
+// precision too, so that a position of many thousands loses nothing.
+__global__ void __launch_bounds__(256)
+add_sinusoid_kernel(float* x, const int* __restrict__ positions, const double* __restrict__ freqs, int C) {
+  pdl_trigger();
+  const int t = blockIdx.x;
+  const double pos = (double)positions[t];
+  pdl_wait();
+  float* o = x + (size_t)t * C;
+  for (int i = threadIdx.x; 2 * i < C; i += blockDim.x) {
+    double sd, cd;
+    sincos(pos * freqs[i], &sd, &cd);
+    o[2 * i] += (float)sd;
+    if (2 * i + 1 < C) o[2 * i + 1] += (float)cd;
+  }
+}
+
+// out[t, d] = act(pre[t, d]) * table[token_t, off + d]: a row's own piece of a second embedding table gates what was
+// made from the row.  A negative token stands for feedback[-token - 1], as in the embedding.
+template <typename T>
+__global__ void __launch_bounds__(256)
+gate_by_table_kernel(const float* pre, int ld, const int* __restrict__ tokens, const int* feedback,
+                     const T* __restrict__ table, int table_ld, int off, int D, int act, T* out, int ldo, int n_rows) {
+  pdl_trigger();
+  const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
+  if (i >= (size_t)n_rows * D) return;
+  const int t = (int)(i / D), d = (int)(i % D);
+  pdl_wait();
+  int tok = tokens[t];
+  if (tok < 0) tok = feedback[-tok - 1];
+  const float e = to_float(table[(size_t)tok * table_ld + off + d]);
+  out[(size_t)t * ldo + d] = from_float<T>(apply_act(pre[(size_t)t * ld + d], act) * e);
+}
+
 __device__ __forceinline__ void store4(float* p, float a, float b, float c, float d) {
   *reinterpret_cast<float4*>(p) = make_float4(a, b, c, d);
 }
@@ -311,6 +346,29 @@ extern "C" int nib_convert(int src_dtype, const void* src, int rows, int cols, i
     convert_kernel<float><<<grid, block, 0, stream>>>(src, src_dtype, rows, cols, (float*)dst, ld, r0, transpose);
   else if (dst_dtype == DT_BF16)
     convert_kernel<bf16><<<grid, block, 0, stream>>>(src, src_dtype, rows, cols, (bf16*)dst, ld, r0, transpose);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
+  NIB_LAUNCH_CHECK();
+}
+
+extern "C" int nib_add_sinusoid(float* x, const int* positions, const double* freqs, int T, int C, cudaStream_t stream) {
+  if (T <= 0 || C <= 0) return 0;
+  launch_pdl(add_sinusoid_kernel, dim3(T), dim3(C >= 512 ? 256 : 128), 0, stream, x, positions, freqs, C);
+  NIB_LAUNCH_CHECK();
+}
+
+extern "C" int nib_gate_by_table(int dtype, const float* pre, int ld, const int* tokens, const int* feedback,
+                                 const void* table, int table_ld, int off, int D, int act, void* out, int ldo,
+                                 int n_rows, cudaStream_t stream) {
+  if (n_rows <= 0 || D <= 0) return 0;
+  const size_t n = (size_t)n_rows * D;
+  const dim3 grid((unsigned)((n + 255) / 256));
+  if (dtype == DT_F32)
+    launch_pdl(gate_by_table_kernel<float>, grid, dim3(256), 0, stream, pre, ld, tokens, feedback, (const float*)table,
+               table_ld, off, D, act, (float*)out, ldo, n_rows);
+  else if (dtype == DT_BF16)
+    launch_pdl(gate_by_table_kernel<bf16>, grid, dim3(256), 0, stream, pre, ld, tokens, feedback, (const bf16*)table,
+               table_ld, off, D, act, (bf16*)out, ldo, n_rows);
   else
     return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();

@@ -83,6 +83,74 @@ rope_append_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, i
   }
 }
 
+// The same step for layers that normalise their queries and keys: every query and key head is divided by its root
+// mean square over `dim` (eps inside the root) and multiplied by a weight of `dim` values that all heads share
+// (wq for queries, wk for keys; null: no norm for that kind), then turned by the position as above, cast, padded and
+// written.  A warp owns a head; lane l owns the pairs l, l + 32, ... of it (at most four: dim <= 256).
+template <typename T>
+__global__ void __launch_bounds__(256)
+norm_rope_append_kernel(const float* proj, int ld, int q_off, int k_off, int v_off, int n_head, int n_kv_head, int dim,
+                        int vdim, int hd, const float* __restrict__ wq, const float* __restrict__ wk, float eps,
+                        int rot_dims, const double* __restrict__ freqs, const int* __restrict__ positions,
+                        const int* __restrict__ row_entry, T* q_out, int ldq, T* cache,
+                        const int* __restrict__ block_table, int max_blocks, int page_size, int n_pages, int* status) {
+  pdl_trigger();
+  const int t = blockIdx.y, lane = threadIdx.x & 31;
+  const int hh = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  if (hh >= n_head + 2 * n_kv_head) return;
+  const int pos = positions[t], entry = row_entry[t];
+  const bool is_q = hh < n_head, is_k = !is_q && hh < n_head + n_kv_head;
+  const int h = is_q ? hh : (is_k ? hh - n_head : hh - n_head - n_kv_head);
+  T* dst = nullptr;
+  if (is_q) {
+    dst = q_out + (size_t)t * ldq + (size_t)h * hd;
+  } else if (entry >= 0 && cache != nullptr) {
+    const int page = block_table[(size_t)entry * max_blocks + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+      if (lane == 0) *status = NIB_STATUS_BAD_PAGE;
+    } else {
+      dst = cache + kv_offset(page, is_k ? 0 : 1, h, pos % page_size, n_kv_head, page_size, hd);
+    }
+  }
+  pdl_wait();
+  if (dst == nullptr) return;
+  const int width = is_q || is_k ? dim : vdim;
+  const float* src = proj + (size_t)t * ld + (is_q ? q_off : (is_k ? k_off : v_off)) + (size_t)h * width;
+  const float* w = is_q ? wq : (is_k ? wk : nullptr);
+  float2 x[4];
+  float ss = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = 2 * (lane + 32 * i);
+    x[i] = c < width ? *reinterpret_cast<const float2*>(src + c) : make_float2(0.0f, 0.0f);
+    ss += x[i].x * x[i].x + x[i].y * x[i].y;
+  }
+  float r = 1.0f;
+  if (w != nullptr) r = 1.0f / sqrtf(warp_sum(ss) / (float)width + eps);
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const int c = 2 * (lane + 32 * i);
+    if (c >= hd) continue;
+    float u = 0.0f, v = 0.0f;
+    if (c < width) {
+      u = x[i].x * r;
+      v = x[i].y * r;
+      if (w != nullptr) {
+        u *= w[c];
+        v *= w[c + 1];
+      }
+      if ((is_q || is_k) && c < rot_dims) {
+        double sd, cd;
+        sincos((double)pos * freqs[c >> 1], &sd, &cd);
+        const float cs = (float)cd, sn = (float)sd, a = u, b = v;
+        u = a * cs - b * sn;
+        v = b * cs + a * sn;
+      }
+    }
+    store_pair<T>(dst + c, u, v);
+  }
+}
+
 }  // namespace nib
 
 using namespace nib;
@@ -111,6 +179,35 @@ extern "C" int nib_rope_append(int dtype, const float* proj, int ld, int q_off, 
     launch_pdl(rope_append_kernel<bf16>, dim3(T), block, 0, stream, proj, ld, q_off, k_off, v_off, n_head, n_kv_head,
                dim, vdim, hd, rot_dims, freqs, positions, row_entry, (bf16*)q_out, ldq, (bf16*)cache, block_table,
                max_blocks, page_size, n_pages, status);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
+  NIB_LAUNCH_CHECK();
+}
+
+// The same with a norm of every query and key head ahead of the rotation (norm_rope_append_kernel): wq and wk hold
+// `dim` values each (either may be null); hd <= 256.
+extern "C" int nib_norm_rope_append(int dtype, const float* proj, int ld, int q_off, int k_off, int v_off, int n_head,
+                                    int n_kv_head, int dim, int vdim, int hd, const float* wq, const float* wk,
+                                    float eps, int rot_dims, const double* freqs, const int* positions,
+                                    const int* row_entry, void* q_out, int ldq, void* cache, const int* block_table,
+                                    int max_blocks, int page_size, int n_pages, int T, int* status,
+                                    cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if ((dim | vdim | hd | rot_dims | ld | ldq | q_off | k_off | v_off) & 1) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (dim <= 0 || vdim <= 0 || dim > hd || vdim > hd || rot_dims < 0 || rot_dims > dim) return NIB_ERR_BAD_ARGUMENT;
+  if (rot_dims > 0 && freqs == nullptr) return NIB_ERR_BAD_ARGUMENT;
+  if (hd > 256 || T > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
+  const int total = n_head + 2 * n_kv_head;
+  const int warps = total < 8 ? total : 8;
+  const dim3 grid((total + warps - 1) / warps, T), block(32 * warps);
+  if (dtype == DT_F32)
+    launch_pdl(norm_rope_append_kernel<float>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off, n_head, n_kv_head,
+               dim, vdim, hd, wq, wk, eps, rot_dims, freqs, positions, row_entry, (float*)q_out, ldq, (float*)cache,
+               block_table, max_blocks, page_size, n_pages, status);
+  else if (dtype == DT_BF16)
+    launch_pdl(norm_rope_append_kernel<bf16>, grid, block, 0, stream, proj, ld, q_off, k_off, v_off, n_head, n_kv_head,
+               dim, vdim, hd, wq, wk, eps, rot_dims, freqs, positions, row_entry, (bf16*)q_out, ldq, (bf16*)cache,
+               block_table, max_blocks, page_size, n_pages, status);
   else
     return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();

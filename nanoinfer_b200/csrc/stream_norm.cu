@@ -126,7 +126,11 @@ add_norm_kernel(float* x, float* y, const float* __restrict__ w_out, const float
     row[c] = v;
     q2 += v * v;
   }
-  if (w_next == nullptr) return;
+  if (xn == nullptr) return;
+  if (w_next == nullptr) {   // the next sublayer reads the stream itself
+    for (int c = threadIdx.x; c < C; c += blockDim.x) xn[base + c] = from_float<OutT>(row[c]);
+    return;
+  }
   const float rstd2 = 1.0f / sqrtf(block_sum(q2, scratch) / (float)C + eps);
   for (int c = threadIdx.x; c < C; c += blockDim.x) xn[base + c] = from_float<OutT>(row[c] * rstd2 * w_next[c]);
 }
@@ -171,9 +175,15 @@ add_norm_rows_kernel(float* x, float* y, const float* __restrict__ w_out, const 
       q2 += v[i].x * v[i].x + v[i].y * v[i].y + v[i].z * v[i].z + v[i].w * v[i].w;
     }
   }
-  if (w_next == nullptr) return;
-  const float rstd2 = 1.0f / sqrtf(warp_sum(q2) / (float)C + eps);
+  if (xn == nullptr) return;
   OutT* o = xn + (size_t)row * C;
+  if (w_next == nullptr) {   // the next sublayer reads the stream itself
+#pragma unroll
+    for (int i = 0; i < NV; ++i)
+      if (lane + 32 * i < n4) store4(o + 4 * (lane + 32 * i), v[i].x, v[i].y, v[i].z, v[i].w);
+    return;
+  }
+  const float rstd2 = 1.0f / sqrtf(warp_sum(q2) / (float)C + eps);
 #pragma unroll
   for (int i = 0; i < NV; ++i) {
     if (lane + 32 * i < n4) {
@@ -198,7 +208,7 @@ glu_kernel(const InT* pre, int ld, OutT* out, int ldo, int n_rows, int F, int ac
   out[(size_t)t * ldo + f] = from_float<OutT>(v);
 }
 
-enum : int { UNARY_TANH = 1, UNARY_XIELU = 2 };
+enum : int { UNARY_TANH = 1, UNARY_XIELU = 2, UNARY_SOFTCAP = 3 };   // softcap: prm[0] tanh(z / prm[0])
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
@@ -212,6 +222,7 @@ unary_kernel(const InT* in, int ld_in, OutT* out, int ld_out, int n_rows, int n_
     sp = softplus_f(prm[0]);
     sq = 0.5f + softplus_f(prm[1]);
   }
+  if (kind == UNARY_SOFTCAP) sp = prm[0];
   pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)n_rows * n_cols) return;
@@ -220,6 +231,8 @@ unary_kernel(const InT* in, int ld_in, OutT* out, int ld_out, int n_rows, int n_
   float y;
   if (kind == UNARY_TANH)
     y = tanhf(z);
+  else if (kind == UNARY_SOFTCAP)
+    y = sp * tanhf(z / sp);
   else
     y = z > 0.0f ? sp * z * z + 0.5f * z : sq * (expm1f(z) - z) + 0.5f * z;
   out[(size_t)r * ld_out + c] = from_float<OutT>(y);
@@ -337,8 +350,8 @@ extern "C" int nib_glu(int in_dtype, int out_dtype, const void* pre, int ld, voi
 extern "C" int nib_unary(int in_dtype, int out_dtype, const void* in, int ld_in, void* out, int ld_out, int n_rows,
                          int n_cols, int kind, const float* prm, cudaStream_t stream) {
   if (n_rows <= 0 || n_cols <= 0) return 0;
-  if (kind != UNARY_TANH && kind != UNARY_XIELU) return NIB_ERR_BAD_ARGUMENT;
-  if (kind == UNARY_XIELU && prm == nullptr) return NIB_ERR_BAD_ARGUMENT;
+  if (kind != UNARY_TANH && kind != UNARY_XIELU && kind != UNARY_SOFTCAP) return NIB_ERR_BAD_ARGUMENT;
+  if (kind != UNARY_TANH && prm == nullptr) return NIB_ERR_BAD_ARGUMENT;
   const size_t n = (size_t)n_rows * n_cols;
   const dim3 grid((unsigned)((n + 255) / 256));
   if (in_dtype == DT_F32 && out_dtype == DT_F32)

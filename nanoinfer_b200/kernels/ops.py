@@ -18,7 +18,7 @@ ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU_SQ, ACT_SILU = 0, 1, 2, 3, 4
 #: (the products' epilogues take all but "silu", which the element-wise and expert kernels apply)
 ACT_CODES = {None: ACT_NONE, "none": ACT_NONE, "tanh": ACT_GELU_TANH, "erf": ACT_GELU_ERF, "relu2": ACT_RELU_SQ,
              "silu": ACT_SILU}
-UNARY_TANH, UNARY_XIELU = 1, 2
+UNARY_TANH, UNARY_XIELU, UNARY_SOFTCAP = 1, 2, 3
 
 STATUS_OK, STATUS_BAD_PAGE, STATUS_WAIT_TIMEOUT = 0, 1, 2
 _ERR_NAMES = {-1: "bad argument", -2: "unsupported size", -3: "CUDA driver call failed"}
@@ -58,10 +58,11 @@ _SIGNATURES = {
     "nib_attention_prefill_tc": [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr,
                                  _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
-                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
+                           _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_float, _c_int,
+                           _c_ptr, _c_ptr, _c_int, _c_float, _c_ptr, _c_ptr],
     "nib_attention_decode": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
-                             _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_int,
-                             _c_int, _c_ptr, _c_ptr, _c_ptr],
+                             _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_float,
+                             _c_int, _c_ptr, _c_ptr, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
     "nib_attention_decode_mma_supported": [_c_int, _c_int],
     "nib_attention_decode_mma_clusters": [_c_int, _c_int],
     "nib_attention_decode_mma": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
@@ -105,6 +106,21 @@ _SIGNATURES = {
     "nib_mlstm": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_float,
                   _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_ptr,
                   _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr],
+    "nib_add_sinusoid": [_c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+    "nib_gate_by_table": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int,
+                          _c_int, _c_ptr],
+    "nib_norm_rope_append": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr,
+                             _c_ptr, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
+                             _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "nib_short_conv": [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, ctypes.c_longlong, _c_ptr, _c_ptr,
+                       _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+    "nib_scan_prepare": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
+                         _c_int, _c_int, _c_ptr, _c_int, _c_ptr],
+    "nib_gated_scan_padded": [_c_int],
+    "nib_gated_scan": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr,
+                       _c_ptr, ctypes.c_longlong, ctypes.c_longlong, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr],
+    "nib_gated_norm": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_float, _c_int, _c_float,
+                       _c_ptr, _c_int, _c_int, _c_ptr],
     "nib_moe_down": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_scale": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_grouped": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
@@ -156,7 +172,8 @@ class _Library:
     def _wrap(name, fn):
         counted = name not in ("nib_linear_tc_supported", "nib_linear_tc_pair_supported", "nib_linear_skinny_supported",
                                "nib_attention_prefill_tc_supported", "nib_attention_prefill_supported",
-                               "nib_attention_decode_mma_supported", "nib_attention_decode_mma_clusters")
+                               "nib_attention_decode_mma_supported", "nib_attention_decode_mma_clusters",
+                               "nib_gated_scan_padded")
 
         def call(*args):
             global _pending_op
@@ -608,9 +625,42 @@ def kv_append(src: torch.Tensor, k_off: int, v_off: int, cache: torch.Tensor, bl
            "kv_append")
 
 
+class AttnExtras:
+    """Options of the attention kernels on the scores and on the output:
+    ``softcap`` > 0: s <- softcap tanh(s / softcap) after the scale; ``slopes`` (float32 [n_head]): s <- s -
+    slopes[h] (query position - key position); ``keep_first``: with a window, the keys 0 .. keep_first - 1 stay
+    visible behind it; ``gate`` (float32 [rows, >= n_head], any row stride): head h's output of row t times
+    sigmoid(gate[t, h]); ``out_scale``: and times this constant."""
+
+    __slots__ = ("softcap", "keep_first", "slopes", "gate", "out_scale")
+
+    def __init__(self, softcap: float = 0.0, keep_first: int = 0, slopes: Optional[torch.Tensor] = None,
+                 gate: Optional[torch.Tensor] = None, out_scale: float = 1.0):
+        self.softcap, self.keep_first, self.slopes = float(softcap), int(keep_first), slopes
+        self.gate, self.out_scale = gate, float(out_scale)
+
+    @property
+    def plain(self) -> bool:
+        return not (self.softcap > 0.0 or self.keep_first > 0 or self.slopes is not None or self.gate is not None
+                    or self.out_scale != 1.0)
+
+    def args(self) -> tuple:
+        g = self.gate
+        if g is not None and (g.dtype != torch.float32 or g.stride(1) != 1):
+            raise KernelError("attention: the output gate must be float32 with contiguous rows")
+        if self.slopes is not None and self.slopes.dtype != torch.float32:
+            raise KernelError("attention: the slopes must be float32")
+        return (self.softcap, self.keep_first, _ptr(self.slopes), _ptr(g), g.stride(0) if g is not None else 0,
+                self.out_scale)
+
+
+_NO_EXTRAS = AttnExtras()
+
+
 def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                    row_entry: torch.Tensor, positions: torch.Tensor, T: int, n_head: int, scale: float,
-                   window: int, status: torch.Tensor, rows: Optional[torch.Tensor] = None, sink: bool = False) -> None:
+                   window: int, status: torch.Tensor, rows: Optional[torch.Tensor] = None, sink: bool = False,
+                   extras: Optional[AttnExtras] = None) -> None:
     """Causal attention of T rows of q ([*, n_head * head_dim], any row stride) over one cache layer, with
     the general kernel (any head size up to 256, any page size).  ``rows`` lists the rows to process."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
@@ -619,7 +669,8 @@ def attention_simt(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bloc
     _check(library().nib_attention_simt(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(out), out.stride(0),
                                         _ptr(block_table), block_table.shape[1], _ptr(rows), _ptr(row_entry),
                                         _ptr(positions), T, n_head, n_kv_head, head_dim, page_size, n_pages,
-                                        float(scale), int(window), int(sink), _ptr(status), _stream()),
+                                        float(scale), int(window), int(sink), *(extras or _NO_EXTRAS).args(),
+                                        _ptr(status), _stream()),
            "attention_simt")
 
 
@@ -716,7 +767,8 @@ def attention_decode_reserve(workspace, n_head: int, head_dim: int) -> None:
 def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                      row_entry: torch.Tensor, positions: torch.Tensor, n_rows: int, n_head: int, scale: float,
                      window: int, status: torch.Tensor, max_keys: int, workspace,
-                     rows: Optional[torch.Tensor] = None, sink: bool = False) -> None:
+                     rows: Optional[torch.Tensor] = None, sink: bool = False,
+                     extras: Optional[AttnExtras] = None) -> None:
     """Split-KV attention for rows that are single decoded tokens.  ``max_keys``: the longest key
     range among them; partial results go through ``workspace``.  bfloat16 with a head size of 32, 64,
     96 or 128 runs on the warp-level MMA kernel, everything else (and float32, in true 32-bit
@@ -724,7 +776,8 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
     if q.dtype != cache.dtype or out.dtype != cache.dtype or q.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("attention: q, out and cache must share a dtype, rows contiguous")
-    mma = USE_DECODE_MMA and q.dtype == torch.bfloat16 and _can("nib_attention_decode_mma_supported", head_dim, page_size) \
+    plain = extras is None or extras.plain     # (the MMA kernel takes no options on the scores or the output)
+    mma = USE_DECODE_MMA and plain and q.dtype == torch.bfloat16 and _can("nib_attention_decode_mma_supported", head_dim, page_size) \
         and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and cache.data_ptr() % 16 == 0
     # (the MMA kernel holds a tile's keys and values in registers: six blocks an SM up to head size 64, three beyond)
     resident = DECODE_RESIDENT_BLOCKS if not mma or head_dim <= 64 else DECODE_RESIDENT_BLOCKS // 2
@@ -758,7 +811,8 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
     _check(library().nib_attention_decode(_dt(q), _ptr(q), q.stride(0), _ptr(cache), _ptr(scratch), _ptr(out),
                                           out.stride(0), _ptr(block_table), block_table.shape[1], _ptr(rows),
                                           _ptr(row_entry), _ptr(positions), n_rows, n_head, n_kv_head, head_dim,
-                                          page_size, n_pages, float(scale), int(window), int(sink), chunk, n_splits,
+                                          page_size, n_pages, float(scale), int(window), int(sink),
+                                          *(extras or _NO_EXTRAS).args(), chunk, n_splits,
                                           _ptr(counters), _ptr(status), _stream()), "attention_decode")
 
 
@@ -796,8 +850,10 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, b
 
 
 def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
-              n_head: int, scale: float, window: int, plan, sink: bool = False) -> None:
-    """Causal attention of the step's rows over one cache layer.  ``sink``: the softmax's denominator has
+              n_head: int, scale: float, window: int, plan, sink: bool = False,
+              extras: Optional[AttnExtras] = None) -> None:
+    """Causal attention of the step's rows over one cache layer.  ``extras``: options on the scores and the output
+    (``AttnExtras``); the kernels that take them are the general one and the streaming split-KV one.  ``sink``: the softmax's denominator has
     one more term, exp(0) (a key of score 0 that has no value; every kernel adds it where it divides).
     ``ctx`` is the step's StepContext, ``plan`` says which rows are single decoded tokens and how the
     prompt portions are cut into tiles (``parts.attention.AttentionPlan``).  Single decoded tokens go to the split-KV kernel;
@@ -805,13 +861,14 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
     16) and to the general kernel otherwise."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
     fast_pages = page_size % 16 == 0 and head_dim % 8 == 0 and head_dim <= 128
+    plain = extras is None or extras.plain
     traced = tracing()   # (the counts leave a window out: they are those of attention over all keys)
     if not fast_pages:
         if traced:
             _note_attention(ctx.n_rows, plan.decode_keys + plan.prefill_keys, plan.decode_keys + plan.prefill_kv_rows,
                             n_head, n_kv_head, head_dim, q.element_size())
         attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions, ctx.n_rows, n_head, scale,
-                       window, ctx.status, sink=sink)
+                       window, ctx.status, sink=sink, extras=extras)
         return
     if plan.n_decode:
         keys = plan.max_decode_keys if window <= 0 else min(plan.max_decode_keys, window)
@@ -819,17 +876,17 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
             _note_attention(plan.n_decode, plan.decode_keys, plan.decode_keys, n_head, n_kv_head, head_dim,
                             q.element_size())
         attention_decode(q, cache, out, block_table, ctx.row_entry, ctx.positions, plan.n_decode, n_head, scale,
-                         window, ctx.status, keys, ctx.workspace, plan.decode_rows, sink=sink)
+                         window, ctx.status, keys, ctx.workspace, plan.decode_rows, sink=sink, extras=extras)
     if plan.n_prefill_rows:
         if traced:
             _note_attention(plan.n_prefill_rows, plan.prefill_keys, plan.prefill_kv_rows, n_head, n_kv_head, head_dim,
                             q.element_size())
-        if q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
+        if plain and q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 \
                 and out.data_ptr() % 16 == 0:
             attention_prefill_tc(q, cache, out, block_table, plan.wide_tiles, plan.n_wide_tiles, ctx.entry_start,
                                  ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status, sink=sink)
-        elif q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
+        elif plain and q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
             attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
                               n_head, scale, window, ctx.status, sink=sink)
@@ -838,7 +895,7 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
             # the launch then depends on the step's shape only, as a graph needs it)
             attention_simt(q, cache, out, block_table, ctx.row_entry, ctx.positions,
                            plan.n_prefill_rows if plan.n_decode else ctx.n_rows, n_head, scale, window, ctx.status,
-                           plan.prefill_rows, sink=sink)
+                           plan.prefill_rows, sink=sink, extras=extras)
 
 
 _SRC_CODES = {torch.float32: 0, torch.bfloat16: 1, torch.float16: 2}
@@ -1253,21 +1310,23 @@ def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: 
 # ----------------------------------------------------------------------------- sublayers normed on both sides
 def add_norm(x: torch.Tensor, y: torch.Tensor, w_out: torch.Tensor, eps: float, n_rows: int,
              w_next: Optional[torch.Tensor] = None, xn: Optional[torch.Tensor] = None) -> None:
-    """x[:n] += y / sqrt(mean(y^2) + eps) * w_out and y[:n] = 0, all in 32-bit; with ``w_next`` also
-    xn[:n] = x / sqrt(mean(x^2) + eps) * w_next in xn's dtype (the next sublayer's input)."""
+    """x[:n] += y / sqrt(mean(y^2) + eps) * w_out and y[:n] = 0, all in 32-bit; with ``xn`` also the next sublayer's
+    input in xn's dtype: xn[:n] = x / sqrt(mean(x^2) + eps) * w_next, or the new x itself where ``w_next`` is None."""
     _f32(x, "add_norm: x"); _f32(y, "add_norm: y"); _f32(w_out, "add_norm: w_out")
     C = x.shape[1]
     if not x.is_contiguous() or not y.is_contiguous() or y.shape[1] != C or w_out.numel() != C:
         raise KernelError("add_norm: x and y contiguous [rows, C], the weights [C]")
     if w_next is not None:
         _f32(w_next, "add_norm: w_next")
-        if xn is None or not xn.is_contiguous() or xn.shape[1] != C or w_next.numel() != C:
-            raise KernelError("add_norm: xn contiguous [rows, C] with w_next [C]")
+        if xn is None or w_next.numel() != C:
+            raise KernelError("add_norm: w_next [C] needs xn")
+    if xn is not None and (not xn.is_contiguous() or xn.shape[1] != C):
+        raise KernelError("add_norm: xn contiguous [rows, C]")
     if tracing():
         _note("ln", "add_norm", (n_rows, C, 0), 10.0 * n_rows * C,
-              n_rows * C * (16.0 + (xn.element_size() if w_next is not None else 0)))
-    _check(library().nib_add_norm(_dt(xn) if w_next is not None else 0, _ptr(x), _ptr(y), _ptr(w_out), _ptr(w_next),
-                                  float(eps), _ptr(xn) if w_next is not None else None, n_rows, C, _stream()), "add_norm")
+              n_rows * C * (16.0 + (xn.element_size() if xn is not None else 0)))
+    _check(library().nib_add_norm(_dt(xn) if xn is not None else 0, _ptr(x), _ptr(y), _ptr(w_out), _ptr(w_next),
+                                  float(eps), _ptr(xn), n_rows, C, _stream()), "add_norm")
 
 
 def glu(pre: torch.Tensor, out: torch.Tensor, n_rows: int, F: int, act: int, row_gate: int = -1) -> None:
@@ -1335,3 +1394,157 @@ def mlstm(proj: torch.Tensor, offsets, bias_i: torch.Tensor, bias_f: torch.Tenso
                                float(cap), _ptr(norm_w), _ptr(state), _ptr(ctx.entry_start), _ptr(ctx.entry_slot),
                                ctx.n_entries, ctx.n_rows, n_head, dim, vdim, float(eps), _ptr(gates), _ptr(num),
                                num.stride(0), _ptr(den), _ptr(out), out.stride(0), _stream()), "mlstm", 3)
+
+
+# ----------------------------------------------------------------------------- sinusoidal positions, a per-token gate
+def add_sinusoid(x: torch.Tensor, positions: torch.Tensor, freqs: torch.Tensor, n_rows: int) -> None:
+    """x[t, 2i] += sin(positions[t] * freqs[i]), x[t, 2i + 1] += cos of the same angle (angles, sines and cosines in
+    double precision); x is the 32-bit stream, freqs float64 [ceil(C / 2)]."""
+    _f32(x, "add_sinusoid: x")
+    _i32(positions, "positions")
+    C = x.shape[1]
+    if not x.is_contiguous() or freqs.dtype != torch.float64 or freqs.numel() < (C + 1) // 2:
+        raise KernelError("add_sinusoid: x contiguous [rows, C], freqs float64 [ceil(C / 2)]")
+    if tracing():
+        _note("embed", "sinusoid", (n_rows, C, 0), 20.0 * n_rows * C, 8.0 * n_rows * C)
+    _check(library().nib_add_sinusoid(_ptr(x), _ptr(positions), _ptr(freqs), n_rows, C, _stream()), "add_sinusoid")
+
+
+def gate_by_table(pre: torch.Tensor, tokens: torch.Tensor, feedback: Optional[torch.Tensor], table: torch.Tensor,
+                  off: int, D: int, act: int, out: torch.Tensor, n_rows: int) -> None:
+    """out[t, d] = act(pre[t, d]) * table[tokens[t], off + d] for d < D; pre is 32-bit, table and out share a dtype.
+    A negative token -(s + 1) stands for ``feedback[s]``, as in ``embed``."""
+    _f32(pre, "gate_by_table: pre")
+    _i32(tokens, "tokens")
+    if table.dtype != out.dtype or table.stride(1) != 1 or out.stride(1) != 1 or pre.stride(1) != 1 \
+            or off < 0 or off + D > table.shape[1] or pre.shape[1] < D or out.shape[1] < D:
+        raise KernelError("gate_by_table: table and out of one dtype, rows contiguous, off + D within the table")
+    if tracing():
+        _note("other", "token_gate", (n_rows, D, 0), 10.0 * n_rows * D, n_rows * D * (4.0 + 2 * out.element_size()))
+    _check(library().nib_gate_by_table(_dt(out), _ptr(pre), pre.stride(0), _ptr(tokens), _ptr(feedback), _ptr(table),
+                                       table.stride(0), int(off), int(D), int(act), _ptr(out), out.stride(0), n_rows,
+                                       _stream()), "gate_by_table")
+
+
+def norm_rope_append(proj: torch.Tensor, offsets, n_head: int, n_kv_head: int, dim: int, vdim: int,
+                     wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float, rot_dims: int,
+                     freqs: Optional[torch.Tensor], ctx, q_out: torch.Tensor, cache: Optional[torch.Tensor],
+                     block_table: Optional[torch.Tensor]) -> None:
+    """``rope_append`` with an RMS norm of every query and key head ahead of the rotation: x / sqrt(mean(x^2) + eps)
+    times a weight of ``dim`` values that the heads share (``wq`` for queries, ``wk`` for keys; None: no norm)."""
+    _f32(proj, "norm_rope_append: proj")
+    hd = q_out.shape[1] // n_head
+    if cache is not None:
+        n_pages, two, g, page_size, chd = cache.shape
+        if two != 2 or g != n_kv_head or chd != hd or not cache.is_contiguous() or cache.dtype != q_out.dtype:
+            raise KernelError("norm_rope_append: cache must be contiguous [pages, 2, kv heads, page, head size] of "
+                              "q_out's dtype")
+        _i32(block_table, "block_table")
+    else:
+        n_pages, page_size = 0, 1
+    for w in (wq, wk):
+        if w is not None and (w.dtype != torch.float32 or w.numel() != dim):
+            raise KernelError("norm_rope_append: a norm weight must be float32 [dim]")
+    if freqs is not None and freqs.dtype != torch.float64:
+        raise KernelError("norm_rope_append: freqs must be float64")
+    if tracing():
+        n = (n_head + 2 * n_kv_head) * hd
+        _note("kv_write", "norm_kv_write", (ctx.n_rows, n, 0), 8.0 * ctx.n_rows * n, ctx.n_rows * n * (4.0 + q_out.element_size()))
+    _check(library().nib_norm_rope_append(
+        _dt(q_out), _ptr(proj), proj.stride(0), offsets[0], offsets[1], offsets[2], n_head, n_kv_head, dim, vdim, hd,
+        _ptr(wq), _ptr(wk), float(eps), rot_dims, _ptr(freqs), _ptr(ctx.positions), _ptr(ctx.row_entry), _ptr(q_out),
+        q_out.stride(0), _ptr(cache), _ptr(block_table), block_table.shape[1] if block_table is not None else 0,
+        page_size, n_pages, ctx.n_rows, _ptr(ctx.status), _stream()), "norm_rope_append")
+
+
+# ----------------------------------------------------------------------------- recurrences with one decay per head
+def gated_scan_padded(n: int) -> int:
+    """The key size ``n`` rounded up to what a variant of the recurrence kernel holds (0: too large)."""
+    return int(library().nib_gated_scan_padded(int(n)))
+
+
+def gated_scan_state_floats(taps: int, channels: int, n_head: int, n: int, v: int) -> int:
+    """Floats of state per request: the convolution's last ``taps - 1`` inputs of ``channels`` values each (rounded up
+    to a multiple of 4), then a matrix [v][n padded] per head."""
+    return -(-(max(taps - 1, 0) * channels) // 4) * 4 + n_head * v * _scan_padded_host(n)
+
+
+def _scan_padded_host(n: int) -> int:
+    for s in (16, 32, 48, 64, 96, 128, 192, 256):
+        if n <= s:
+            return s
+    return 0
+
+
+def short_conv(proj: torch.Tensor, c_off: int, channels: int, taps: int, w: torch.Tensor, bias: Optional[torch.Tensor],
+               state: torch.Tensor, ctx, out: torch.Tensor, act: int) -> None:
+    """out[t, c] = act(bias[c] + sum_j w[c, j] x[t - (taps - 1 - j), c]) over the columns c_off .. of the 32-bit
+    ``proj``, per batch entry in row order; what lies before an entry's first row comes from the first
+    (taps - 1) * channels floats of the request's row of ``state`` (oldest first), which then moves on by the
+    entry's rows.  A step in which every entry is one row does both in one launch."""
+    _f32(proj, "short_conv: proj"); _f32(state, "short_conv: state"); _f32(out, "short_conv: out"); _f32(w, "short_conv: w")
+    if w.shape != (channels, taps) or not w.is_contiguous() or proj.stride(1) != 1 or out.stride(1) != 1 \
+            or state.stride(1) != 1 or out.shape[1] < channels:
+        raise KernelError("short_conv: w contiguous [channels, taps], rows of proj, out and state contiguous")
+    T, E = ctx.n_rows, ctx.n_entries
+    fused = int(T == E)      # (every entry has a row, so as many rows as entries means one each)
+    if tracing():
+        _note("other", "short_conv", (T, channels, taps), 2.0 * T * channels * taps, 8.0 * T * channels)
+    _check(library().nib_short_conv(_ptr(proj), proj.stride(0), int(c_off), int(channels), int(taps), _ptr(w),
+                                    _ptr(bias), _ptr(state), state.stride(0), _ptr(ctx.row_entry), _ptr(ctx.entry_start),
+                                    _ptr(ctx.entry_slot), _ptr(out), out.stride(0), T, E, int(act), fused, _stream()),
+           "short_conv", 1 if fused or taps <= 1 else 2)
+
+
+def scan_prepare(proj: torch.Tensor, a_off: int, w_off: int, A_log: torch.Tensor, dt_bias: torch.Tensor,
+                 cv: torch.Tensor, q_off: int, k_off: int, n: int, n_head: int, n_kq: int, delta: bool,
+                 coef: torch.Tensor, n_rows: int) -> None:
+    """coef[t, h] = (decay, strength) of every row and head, from the 32-bit projections; for the delta rule also
+    the query and key heads of ``cv`` made unit vectors in place (queries times n^-1/2)."""
+    _f32(proj, "scan_prepare: proj"); _f32(cv, "scan_prepare: cv"); _f32(coef, "scan_prepare: coef")
+    _f32(A_log, "scan_prepare: A_log"); _f32(dt_bias, "scan_prepare: dt_bias")
+    if tracing():
+        _note("other", "scan_prepare", (n_rows, n_head, 0), 40.0 * n_rows * n_head, 16.0 * n_rows * n_head)
+    _check(library().nib_scan_prepare(_ptr(proj), proj.stride(0), int(a_off), int(w_off), _ptr(A_log), _ptr(dt_bias),
+                                      _ptr(cv), cv.stride(0), int(q_off), int(k_off), int(n), int(n_head), int(n_kq),
+                                      int(bool(delta)), _ptr(coef), n_rows, _stream()), "scan_prepare")
+
+
+def gated_scan(delta: bool, cv: torch.Tensor, q_off: int, k_off: int, v_off: int, n: int, v: int, n_head: int,
+               kq_ratio: int, coef: torch.Tensor, skip: Optional[torch.Tensor], state: torch.Tensor, s_off: int, ctx,
+               out: torch.Tensor) -> None:
+    """The recurrence over the step's rows, entry by entry in row order, per head with S [n x v], decay a and
+    strength w of the row:  delta rule: S <- a S; u = w (v - S^T k); S <- S + k u^T; o = S^T q;
+    state space: S <- a S + k (w v)^T; o = S^T q + skip[h] v.  ``cv`` holds the rows' vectors (q of key/query head g
+    at q_off + g n, k at k_off + g n, v of head h at v_off + h v; head h reads key/query head h // kq_ratio);
+    the matrices live at ``s_off`` floats into each request's row of ``state``; out [rows, n_head * v] float32."""
+    _f32(cv, "gated_scan: cv"); _f32(coef, "gated_scan: coef"); _f32(state, "gated_scan: state"); _f32(out, "gated_scan: out")
+    if state.stride(1) != 1 or cv.stride(1) != 1 or out.stride(1) != 1:
+        raise KernelError("gated_scan: rows of cv, state and out must be contiguous")
+    if tracing():
+        T = ctx.n_rows
+        _note("scan", "gated_scan", (T, n_head * n, n_head * v), (8.0 if delta else 6.0) * T * n_head * n * v,
+              4.0 * T * n_head * (2 * n + 2 * v) + 8.0 * ctx.n_entries * n_head * n * v)
+    _check(library().nib_gated_scan(int(bool(delta)), _ptr(cv), cv.stride(0), int(q_off), int(k_off), int(v_off), int(n),
+                                    int(v), int(n_head), int(kq_ratio), _ptr(coef), _ptr(skip), _ptr(state),
+                                    state.stride(0), int(s_off), _ptr(ctx.entry_start), _ptr(ctx.entry_slot),
+                                    ctx.n_entries, _ptr(out), out.stride(0), _stream()), "gated_scan")
+
+
+def gated_norm(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tensor, n_groups: int, group_size: int,
+               eps: float, gate_first: bool, out_scale: float, out: torch.Tensor, n_rows: int) -> None:
+    """Per row and group of ``group_size`` values: y = o (times silu(gate) first where ``gate_first``), over its root
+    mean square, times weight[(index in the row) mod len(weight)] (times silu(gate) afterwards otherwise), times
+    ``out_scale``, in out's dtype.  o and gate are 32-bit."""
+    _f32(o, "gated_norm: o"); _f32(weight, "gated_norm: weight")
+    if gate is not None and gate.dtype != torch.float32:
+        raise KernelError("gated_norm: gate must be float32")
+    if o.stride(1) != 1 or out.stride(1) != 1 or (gate is not None and gate.stride(1) != 1):
+        raise KernelError("gated_norm: rows must be contiguous")
+    if tracing():
+        n = n_groups * group_size
+        _note("ln", "gated_norm", (n_rows, n, 0), 12.0 * n_rows * n, n_rows * n * (8.0 + out.element_size()))
+    _check(library().nib_gated_norm(_dt(out), _ptr(o), o.stride(0), _ptr(gate), gate.stride(0) if gate is not None else 0,
+                                    _ptr(weight), weight.numel(), int(n_groups), int(group_size), float(eps),
+                                    int(bool(gate_first)), float(out_scale), _ptr(out), out.stride(0), n_rows, _stream()),
+           "gated_norm")

@@ -87,7 +87,8 @@ class Model:
                 # (a reader may look back over a window of its own: the owner's pages are kept for the widest)
                 a = self._kv_spec(e.layer)
                 b = self._kv_spec(self.schedule[e.cache_of].layer)
-                if a is None or b is None or dataclasses.replace(a, window=0) != dataclasses.replace(b, window=0):
+                if a is None or b is None or dataclasses.replace(a, window=0, keep_first=0) != \
+                        dataclasses.replace(b, window=0, keep_first=0):
                     raise ValueError(f"schedule[{i}] cannot read the cache of entry {e.cache_of}: "
                                      f"their key/value needs differ ({a} vs {b})")
 
@@ -127,14 +128,16 @@ class Model:
     def kv_needs(self) -> List[Tuple[int, P.KVCacheSpec]]:
         """(schedule index, need) for every run that owns paged keys and values.  Where other runs read
         an owner's cache through windows of their own, the owner's pages are kept for the widest of them
-        (0, all keys, being the widest)."""
+        (0, all keys, being the widest), and as many first positions stay behind the window as any of them asks."""
         out = []
         for i, e in enumerate(self.schedule):
             spec = self._kv_spec(e.layer)
             if spec is not None and e.cache_of is None:
-                windows = [spec.window] + [self._kv_spec(r.layer).window for r in self.schedule if r.cache_of == i]
+                readers = [spec] + [self._kv_spec(r.layer) for r in self.schedule if r.cache_of == i]
+                windows = [r.window for r in readers]
                 widest = 0 if min(windows) <= 0 else max(windows)
-                out.append((i, dataclasses.replace(spec, window=widest)))
+                kept = max(r.keep_first for r in readers) if widest > 0 else 0
+                out.append((i, dataclasses.replace(spec, window=widest, keep_first=kept)))
         return out
 
     def state_needs(self) -> List[Tuple[int, P.StateSpec]]:

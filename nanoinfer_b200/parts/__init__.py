@@ -1,7 +1,7 @@
 """The parts a model is put together from.  Importing this package registers the built-in
 parts under their names."""
-from . import (attention, block, delta_rule, depth_mix, embedding, head, latent_attention, mlp, mlstm, norm,  # noqa: F401
-               position, routed)  # (registration)
+from . import (attention, block, delta_rule, depth_mix, embedding, gated_scan, head, latent_attention, mlp, mlstm,  # noqa: F401
+               norm, position, routed)  # (registration)
 from .base import (DEPTH_MIXES, FEED_FORWARDS, HEADS, EMBEDDINGS, MIXERS, NORMS, POSITIONS, DepthMix, Embedding, FeedForward, Head,
                    KVCacheSpec, KVCacheView, Mixer, Norm, ParamSpec, Part, PositionEncoding, StateSpec,
                    StepContext, TensorRef, Workspace, register_depth_mix, register_embedding, register_feed_forward,

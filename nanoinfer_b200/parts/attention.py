@@ -16,7 +16,7 @@ from typing import List, Optional
 import torch
 
 from ..kernels import ops
-from .base import (MATRIX, VECTOR, KVCacheSpec, KVCacheView, Mixer, ParamSpec, PositionEncoding, StepContext,
+from .base import (INIT_ONE_PLUS_NORMAL, MATRIX, VECTOR, KVCacheSpec, KVCacheView, Mixer, ParamSpec, PositionEncoding, StepContext,
                    StepLimits, StepPlan, Workspace, register_mixer)
 
 #: a plan made for a graph rounds the longest key range of the decoded rows up to this many positions:
@@ -220,7 +220,12 @@ class GeneralAttention(CausalSelfAttention):
             p[key] = w[at:at + n]
             at += n
         self.w_qkv = w
-        # the output projection reads heads of the cache's size: zero columns where a value head is shorter
+        self._pad_out_weight()
+
+    def _pad_out_weight(self) -> None:
+        """The output projection reads heads of the cache's size: zero columns where a value head is shorter."""
+        p = self.params
+        w = p["out_weight"]
         if self.v_dim == self.cache_dim:
             self.w_out = p["out_weight"]
         else:
@@ -262,3 +267,123 @@ class GeneralAttention(CausalSelfAttention):
                       sink=self.sink)
         ops.trace_scope(ctx.layer, "attn_proj")
         ops.linear(att, self.w_out, None, x, T, residual=True)
+
+
+@register_mixer("normed_attention")
+class NormedAttention(GeneralAttention):
+    """``general_attention`` with what some designs put around the scores, each an option of its own:
+
+    * ``bias``: q, k, v and the output projection have biases;
+    * ``qk_norm``: every query and key head is divided by its root mean square over ``head_dim`` (``eps`` inside the
+      root) and multiplied by a weight of ``head_dim`` values that all heads share (one for queries, one for keys),
+      ahead of the rotation (if any) and of the cache, so the cache holds normed keys;
+    * ``softcap`` > 0: s <- softcap * tanh(s / softcap) after the scale;
+    * ``distance_bias`` = b: s <- s - slope_h * (i - j) with slope_h = 2^(-b (h + 1) / n_head) for query head h;
+    * ``window`` with ``keep_first``: position i sees j <= i with i - j < window or j < keep_first;
+    * ``head_gate``: head h's output is multiplied by sigmoid(W_g x)_h, one number per row and head;
+    * ``out_scale``: the mixer's whole output times a constant (applied to the heads' outputs, and to the bias);
+    * ``own_kv`` False: the layer has no key and value tensors (projections, biases, key norm) at all: it only ever
+      runs on another run's cache.
+
+    One product makes [q | gate | k | v] (+ biases) as 32-bit floats; one kernel norms, turns, casts and writes
+    queries to the attention's input and keys and values into the cache.  The attention kernels that take the
+    options on the scores are the general one (prompt portions) and the streaming split-KV one (single tokens)."""
+
+    def __init__(self, width: int, n_head: int, n_kv_head: int, head_dim: int, v_dim: int, scale: float, eps: float,
+                 window: int = 0, keep_first: int = 0, sink: bool = False, bias: bool = False, qk_norm: bool = True,
+                 softcap: float = 0.0, distance_bias: Optional[float] = None, head_gate: bool = False,
+                 out_scale: float = 1.0, own_kv: bool = True, position: Optional[PositionEncoding] = None):
+        super().__init__(width, n_head, n_kv_head, head_dim, v_dim, scale, window, sink, position)
+        if keep_first < 0 or softcap < 0.0:
+            raise ValueError("normed_attention: keep_first and softcap must not be negative")
+        self.bias = bool(bias)
+        self.eps, self.keep_first, self.qk_norm, self.softcap = float(eps), int(keep_first), bool(qk_norm), float(softcap)
+        self.distance_bias = None if distance_bias is None else float(distance_bias)
+        self.head_gate, self.out_scale, self.own_kv = bool(head_gate), float(out_scale), bool(own_kv)
+        self.n_g = self.n_head if self.head_gate else 0
+        #: columns of the fused projection's output: q | gate | k | v; the first two (a multiple of 8 wide) are all
+        #: that a run on another run's cache needs
+        self.n_qg = _round_up(self.n_q + self.n_g, 8)
+        self.k_off, self.v_off = self.n_qg, self.n_qg + self.n_k
+        self.n_proj = _round_up(self.n_qg + self.n_k + self.n_v, 8) if self.own_kv else self.n_qg
+        self.slopes: Optional[torch.Tensor] = None
+
+    def param_specs(self) -> List[ParamSpec]:
+        c = self.width
+        specs = [ParamSpec("q_weight", (self.n_q, c), MATRIX),
+                 ParamSpec("out_weight", (c, self.n_head * self.v_dim), MATRIX)]
+        if self.own_kv:
+            specs += [ParamSpec("k_weight", (self.n_k, c), MATRIX), ParamSpec("v_weight", (self.n_v, c), MATRIX)]
+        if self.bias:
+            specs += [ParamSpec("q_bias", (self.n_q,), VECTOR), ParamSpec("out_bias", (c,), VECTOR)]
+            if self.own_kv:
+                specs += [ParamSpec("k_bias", (self.n_k,), VECTOR), ParamSpec("v_bias", (self.n_v,), VECTOR)]
+        if self.qk_norm:
+            specs.append(ParamSpec("q_norm", (self.key_dim,), VECTOR, INIT_ONE_PLUS_NORMAL))
+            if self.own_kv:
+                specs.append(ParamSpec("k_norm", (self.key_dim,), VECTOR, INIT_ONE_PLUS_NORMAL))
+        if self.head_gate:
+            specs.append(ParamSpec("gate_weight", (self.n_head, c), MATRIX))
+        return specs
+
+    def kv_spec(self) -> Optional[KVCacheSpec]:
+        return KVCacheSpec(self.n_kv_head, self.cache_dim, self.window,
+                           keep_first=self.keep_first if self.window > 0 else 0)
+
+    def prepare(self, dtype, device) -> None:
+        Mixer.prepare(self, dtype, device)
+        p = self.params
+        q = p["q_weight"]
+        w = torch.zeros(self.n_proj, self.width, dtype=q.dtype, device=q.device)
+        b = torch.zeros(self.n_proj, dtype=torch.float32, device=q.device) if self.bias else None
+        places = [("q", 0), ("gate", self.n_q)] + ([("k", self.k_off), ("v", self.v_off)] if self.own_kv else [])
+        for name, at in places:
+            if name + "_weight" not in p:
+                continue
+            n = p[name + "_weight"].shape[0]
+            w[at:at + n] = p[name + "_weight"]
+            p[name + "_weight"] = w[at:at + n]
+            if b is not None and name + "_bias" in p:
+                b[at:at + n] = p[name + "_bias"]
+                p[name + "_bias"] = b[at:at + n]
+        self.w_qkv, self.b_qkv = w, b
+        self._pad_out_weight()
+        self.out_bias = p["out_bias"] * self.out_scale if self.bias else None
+        if self.distance_bias is not None:
+            h = torch.arange(1, self.n_head + 1, dtype=torch.float64)
+            self.slopes = (2.0 ** (-self.distance_bias * h / self.n_head)).to(torch.float32).to(device)
+
+    def reserve(self, workspace: Workspace, limits: StepLimits) -> None:
+        super().reserve(workspace, limits)
+        workspace.reserve("attention.proj32", limits.max_rows * max(self.n_proj, self.n_qg), torch.float32)
+
+    def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: Optional[KVCacheView],
+                state: Optional[torch.Tensor], writes_cache: bool = True) -> None:
+        if cache is None:
+            raise ValueError("normed_attention needs a paged cache")
+        if writes_cache and not self.own_kv:
+            raise ValueError("normed_attention: a layer without key and value tensors can only read another run's cache")
+        if isinstance(xn, ops.NormInput):
+            xn = xn.materialise(ctx.n_rows)
+        T, ws, p = ctx.n_rows, ctx.workspace, self.params
+        n = self.n_proj if writes_cache else self.n_qg
+        proj = ws.get("attention.proj32", (ctx.max_rows, n), torch.float32)
+        ops.trace_scope(ctx.layer, "qkv")
+        ops.linear(xn, self.w_qkv[:n], None if self.b_qkv is None else self.b_qkv[:n], proj, T)
+        q = ws.get("attention.q", (ctx.max_rows, self.q_dim), self.dtype)
+        pos = self.position
+        ops.norm_rope_append(proj, (0, self.k_off, self.v_off), self.n_head, self.n_kv_head, self.key_dim, self.v_dim,
+                             p.get("q_norm"), p.get("k_norm") if writes_cache else None, self.eps,
+                             pos.dims if pos is not None else 0, pos.freqs if pos is not None else None, ctx, q,
+                             cache.layer if writes_cache else None, cache.block_table if writes_cache else None)
+        att = ws.get("attention.out", (ctx.max_rows, self.q_dim), self.dtype)
+        plan = ctx.plans.get("causal_attention")
+        if plan is None:
+            plan = ctx.plans["causal_attention"] = AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0,
+                                                                 device=x.device)
+        extras = ops.AttnExtras(self.softcap, self.keep_first if self.window > 0 else 0, self.slopes,
+                                proj[:, self.n_q:self.n_q + self.n_g] if self.head_gate else None, self.out_scale)
+        ops.attention(q, cache.layer, att, cache.block_table, ctx, self.n_head, self.scale, self.window, plan,
+                      sink=self.sink, extras=extras)
+        ops.trace_scope(ctx.layer, "attn_proj")
+        ops.linear(att, self.w_out, self.out_bias, x, T, residual=True)

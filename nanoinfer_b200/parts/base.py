@@ -55,6 +55,8 @@ class KVCacheSpec:
     window: int = 0          # 0: all keys; w > 0: the last w positions only
     #: tensors per position and head: 2 (a key and a value), or 1 where one row serves as both (a latent)
     planes: int = 2
+    #: with a window: the positions 0 .. keep_first - 1 stay readable behind it (their pages are never given back)
+    keep_first: int = 0
 
 
 @dataclass(frozen=True)

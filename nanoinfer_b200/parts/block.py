@@ -193,3 +193,61 @@ class SandwichNormBlock(Block):
             ctx.stream_entered = True
         ops.add_norm(x, y, last.params["weight"], self.eps, T, nxt.norm_1.params["weight"] if fuse else None,
                      xn if fuse else None)
+
+
+@register_block("output_norm")
+class OutputNormBlock(Block):
+    """A norm on each sublayer's OUTPUT only, ahead of the sum; the sublayers read the stream itself:
+        x <- x + norm_1(mixer(x));   x <- x + norm_2(feed_forward(x));   x <- x + norm_3(token_input(x))
+    (the second and the third line only where the layer has that part; ``token_input`` is any row-wise part that
+    also reads the rows' tokens).  All are RMS norms with one eps.
+
+    A sublayer reads the stream cast to the engine's dtype and adds its products into a 32-bit buffer of its own
+    that it finds zero.  Between two sublayers runs ONE kernel: the norm of that buffer, the sum into the stream,
+    the buffer zeroed again, and the cast of the new stream that the next sublayer reads, also for the next layer
+    where that is of this arrangement (``ctx.stream_entered`` then tells it that its input is ready)."""
+
+    slots = {"mixer": MIXERS, "norm_1": NORMS, "feed_forward": FEED_FORWARDS, "norm_2": NORMS,
+             "token_input": FEED_FORWARDS, "norm_3": NORMS}
+    optional = ("feed_forward", "norm_2", "token_input", "norm_3")
+
+    def __init__(self, width: int, parts: Dict[str, Part]):
+        super().__init__(width, parts)
+        for a, b in (("feed_forward", "norm_2"), ("token_input", "norm_3")):
+            if (a in parts) != (b in parts):
+                raise ValueError(f"output_norm: {a} and {b} come together or not at all")
+        norms = [parts[n] for n in ("norm_1", "norm_2", "norm_3") if n in parts]
+        if any(not hasattr(n, "eps") or "bias" in {s.key for s in n.param_specs()} for n in norms):
+            raise ValueError("output_norm: its norms must be RMS norms")
+        if len({n.eps for n in norms}) != 1:
+            raise ValueError("output_norm: its norms share one eps")
+        self.eps = norms[0].eps
+        #: (sublayer, the norm of its output), in run order
+        self.sublayers = [(parts["mixer"], parts["norm_1"])]
+        self.sublayers += [(parts[a], parts[b]) for a, b in (("feed_forward", "norm_2"), ("token_input", "norm_3"))
+                           if a in parts]
+
+    def reserve(self, workspace, limits) -> None:
+        workspace.reserve("block.normed", limits.max_rows * self.width, limits.dtype)
+        workspace.reserve("block.sublayer", limits.max_rows * self.width, torch.float32, zeroed=True)
+
+    def forward(self, x, ctx, cache, state, writes_cache, dtype) -> None:
+        T, ws = ctx.n_rows, ctx.workspace
+        xn = ws.get("block.normed", (ctx.max_rows, self.width), dtype)
+        # zero when first handed out, and zeroed again by every kernel that reads it
+        y = ws.get_zeroed("block.sublayer", (ctx.max_rows, self.width), torch.float32)
+        if ctx.stream_entered:
+            ctx.stream_entered = False      # the arrangement before this one left the cast stream behind
+        else:
+            ops.stream_enter(x, xn, 1.0, T)
+        nxt = ctx.next_block
+        fuse = isinstance(nxt, OutputNormBlock) and nxt.width == self.width
+        for i, (part, norm) in enumerate(self.sublayers):
+            if i == 0:
+                part.forward(xn, y, ctx, cache, state, writes_cache)
+            else:
+                part.forward(xn, y, ctx)
+            last = i + 1 == len(self.sublayers)
+            ops.add_norm(x, y, norm.params["weight"], self.eps, T, None, None if last and not fuse else xn)
+        if fuse:
+            ctx.stream_entered = True

@@ -39,13 +39,22 @@ class LayerNorm(Norm):
 
 @register_norm("rmsnorm")
 class RMSNorm(Norm):
-    """x / sqrt(mean(x^2) + eps) * weight, the eps inside the root; statistics in 32-bit."""
+    """x / sqrt(mean(x^2) + eps) * weight, the eps inside the root; statistics in 32-bit.  ``one_plus``: the
+    checkpoint stores the weight around zero and the norm multiplies by 1 + w; the one is added once, after
+    loading, in 32-bit, so that every kernel sees a plain weight."""
 
-    def __init__(self, width: int, eps: float):
-        self.width, self.eps = int(width), float(eps)
+    def __init__(self, width: int, eps: float, one_plus: bool = False):
+        self.width, self.eps, self.one_plus = int(width), float(eps), bool(one_plus)
+        self._shifted = False
 
     def param_specs(self) -> List[ParamSpec]:
-        return [ParamSpec("weight", (self.width,), VECTOR, INIT_ONE_PLUS_NORMAL)]
+        return [ParamSpec("weight", (self.width,), VECTOR, INIT_NORMAL if self.one_plus else INIT_ONE_PLUS_NORMAL)]
+
+    def prepare(self, dtype, device) -> None:
+        super().prepare(dtype, device)
+        if self.one_plus and not self._shifted:
+            self.params["weight"] = self.params["weight"] + 1.0
+            self._shifted = True
 
     def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int,
                 rows: Optional[torch.Tensor] = None) -> None:

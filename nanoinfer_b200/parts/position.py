@@ -51,3 +51,25 @@ class RotaryPairs(PositionEncoding):
     def on_qk(self, q, k, ctx) -> None:
         raise NotImplementedError("rotary_pairs turns queries and keys inside ops.rope_append, on the projection's "
                                   "32-bit output; a mixer that holds it calls that")
+
+
+@register_position("sinusoidal")
+class SinusoidalPositions(PositionEncoding):
+    """Fixed sinusoidal positions added to the embedding: entry 2i of a row at position p gets
+    sin(p * base^(-2i / width)), entry 2i + 1 the cosine of the same angle.  No parameters and no table: the
+    frequencies are made in double precision on the host, and one kernel makes angle, sine and cosine in double
+    precision from the row's position, so no length bounds the context."""
+
+    def __init__(self, width: int, base: float = 10000.0):
+        if width <= 0 or not base > 0.0:
+            raise ValueError("sinusoidal: width and base must be positive")
+        self.width, self.base = int(width), float(base)
+        self.freqs: Optional[torch.Tensor] = None
+
+    def prepare(self, dtype, device) -> None:
+        super().prepare(dtype, device)
+        i = torch.arange((self.width + 1) // 2, dtype=torch.float64)
+        self.freqs = (self.base ** (-2.0 * i / self.width)).to(device)
+
+    def on_embedding(self, x, ctx) -> None:
+        ops.add_sinusoid(x, ctx.positions, self.freqs, ctx.n_rows)

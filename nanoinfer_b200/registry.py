@@ -81,5 +81,10 @@ def _register_builtin() -> None:
 
     register_architecture("Mulavik", MulavikConfig, build_mulavik_spec)
 
+    from .config.kemuzen import KemuzenConfig
+    from .models.kemuzen import build_kemuzen_spec
+
+    register_architecture("Kemuzen", KemuzenConfig, build_kemuzen_spec)
+
 
 _register_builtin()
