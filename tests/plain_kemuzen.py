@@ -78,7 +78,7 @@ def visible(n: int, size: Optional[int], keep_first: int) -> torch.Tensor:
 # --------------------------------------------------------------------------- mixers
 def capped_attention_kv(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float):
     """Keys (after their norm) and values of a capped-attention layer: what its cache holds."""
-    n, G, d, dv = h.shape[0], m["kv_heads"], m["dim"], m["vdim"]
+    n, G, d, dv = h.shape[0], (m.get("kv_heads") or m["heads"]), m["dim"], m["vdim"]
     k = (h @ W[p + "k"].T + W[p + "k.b"]).view(n, G, d)
     v = (h @ W[p + "v"].T + W[p + "v.b"]).view(n, G, dv)
     return heads_rms(k, W[p + "k.norm"], eps), v
@@ -88,7 +88,7 @@ def capped_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float,
     """Attention with biases, query/key norm per head, no rotation, scores (q . k) scale squashed by
     cap tanh(s / cap), a sliding window that also keeps the first tokens, ordinary softmax.  ``kv``: another
     layer's (keys, values) to read instead of this layer's own."""
-    n, H, G, d, dv = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    n, H, G, d, dv = h.shape[0], m["heads"], (m.get("kv_heads") or m["heads"]), m["dim"], m["vdim"]
     q = heads_rms((h @ W[p + "q"].T + W[p + "q.b"]).view(n, H, d), W[p + "q.norm"], eps)
     k, v = kv if kv is not None else capped_attention_kv(h, W, p, m, eps)
     mask = m.get("mask") or {}
@@ -108,7 +108,7 @@ def distance_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: floa
     """Attention without biases, query/key norm per head, scores (q . k) scale - slope_a (i - j) with
     slope_a = 2^(-8 (a + 1) / H), a plain sliding window, softmax, every head's output times the sigmoid of
     one number of its own."""
-    n, H, G, d, dv = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    n, H, G, d, dv = h.shape[0], m["heads"], (m.get("kv_heads") or m["heads"]), m["dim"], m["vdim"]
     q = heads_rms((h @ W[p + "q"].T).view(n, H, d), W[p + "q.norm"], eps)
     k = heads_rms((h @ W[p + "k"].T).view(n, G, d), W[p + "k.norm"], eps)
     v = (h @ W[p + "v"].T).view(n, G, dv)
@@ -127,7 +127,7 @@ def distance_attention(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: floa
 def gated_delta(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
     """The gated delta rule, token by token.  Per head, with unit q (times dim^-1/2) and k:
         S <- g S;  u = beta (v - S^T k);  S <- S + k u^T;  o = S^T q."""
-    n, H, G, d, dv = h.shape[0], m["heads"], m["kv_heads"], m["dim"], m["vdim"]
+    n, H, G, d, dv = h.shape[0], m["heads"], (m.get("kv_heads") or m["heads"]), m["dim"], m["vdim"]
     q = silu(short_conv(h @ W[p + "q"].T, W[p + "q.conv"])).view(n, G, d)
     k = silu(short_conv(h @ W[p + "k"].T, W[p + "k.conv"])).view(n, G, d)
     v = silu(short_conv(h @ W[p + "v"].T, W[p + "v.conv"])).view(n, H, dv)
@@ -153,7 +153,7 @@ def state_space(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> t
     """Mamba-2, token by token.  W_in h = [z | x | B | C | dt]; x, B, C through the short convolution (with a
     bias) and silu; dt = softplus(dt + dt_bias); per head S <- exp(-exp(A_log) dt) S + dt B x^T (S is
     state x vdim), y = S^T C + D x; then y silu(z), RMS norm in groups, the weight, W_o."""
-    n, H, dv, N, G = h.shape[0], m["heads"], m["vdim"], m["state"], m["groups"]
+    n, H, dv, N, G = h.shape[0], m["heads"], m["vdim"], m["state"], (m.get("groups") or 1)
     inner = H * dv
     u = h @ W[p + "in"].T
     z, xbc, dt = u[:, :inner], u[:, inner:2 * inner + 2 * G * N], u[:, 2 * inner + 2 * G * N:]
@@ -170,14 +170,14 @@ def state_space(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> t
             S = torch.exp(-torch.exp(W[p + "A_log"][a]) * dt[t, a]) * S + dt[t, a] * torch.outer(B[t, g], x[t, a])
             y[t, a] = S.T @ C[t, g] + W[p + "D"][a] * x[t, a]
     y = y.reshape(n, inner) * silu(z)
-    parts = m["norm_groups"]
+    parts = m.get("norm_groups") or 1
     y = rms(y.view(n, parts, inner // parts), eps).reshape(n, inner) * W[p + "norm"]
     return y @ W[p + "o"].T
 
 
 def side_by_side(h, W: Dict[str, torch.Tensor], p: str, m: dict, eps: float) -> torch.Tensor:
-    return (m["left_scale"] * distance_attention(h, W, p + "left.", m["left"], eps)
-            + m["right_scale"] * state_space(h, W, p + "right.", m["right"], eps))
+    return (m.get("left_scale", 1.0) * distance_attention(h, W, p + "left.", m["left"], eps)
+            + m.get("right_scale", 1.0) * state_space(h, W, p + "right.", m["right"], eps))
 
 
 # --------------------------------------------------------------------------- feed-forward, token input
@@ -241,3 +241,15 @@ class PlainKemuzen:
         if cfg.get("logit_softcap"):
             logits = capped(logits, float(cfg["logit_softcap"]))
         return (logits, torch.stack(layers)) if return_layers else logits
+
+    def logits(self, tokens: Sequence[int]) -> torch.Tensor:
+        return self.forward(tokens)
+
+    def greedy(self, prompt: Sequence[int], n_new: int) -> List[int]:
+        """The prompt's greedy continuation, the whole sequence run again for every new token."""
+        seq, out = list(prompt), []
+        for _ in range(n_new):
+            nxt = int(self.forward(seq)[-1].argmax())
+            out.append(nxt)
+            seq.append(nxt)
+        return out
