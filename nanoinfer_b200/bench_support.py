@@ -447,6 +447,36 @@ def mulavik_like(width: int, n_layer: int, vocab: int) -> dict:
                 norm=dict(eps=1e-6), layers=layers)
 
 
+def kemuzen_like(width: int, n_layer: int, vocab: int, window: int = 512) -> dict:
+    """A Kemuzen configuration whose layers have the sizes of a GPT-2 of ``width`` (heads of 64; a gated feed-forward
+    of 8/3 x width, which has the parameters of a plain one of 4 x width): by turns a gated-delta-rule layer, a layer
+    with windowed distance-bias attention beside a Mamba-2 recurrence (state 64), a capped attention layer whose
+    window keeps the first four tokens (a key/value head for about four query heads), and one that reads the keys
+    and values of the layer before; a token input of 32 values in every layer."""
+    heads = width // 64
+    kv_heads = max(d for d in range(1, max(1, heads // 4) + 1) if heads % d == 0)
+    att = dict(heads=heads, kv_heads=kv_heads, dim=64, vdim=64, scale=0.125, softcap=30.0,
+               mask=dict(size=window, keep_first=4))
+    left = dict(heads=heads, kv_heads=kv_heads, dim=64, vdim=64, scale=0.125, mask=dict(size=window))
+    right = dict(heads=heads, vdim=64, state=64, groups=1, norm_groups=1, conv=4)
+    delta = dict(heads=heads, kv_heads=heads, dim=64, vdim=64, conv=4)
+    dense = dict(kind="dense", ff=-(-(8 * width // 3) // 64) * 64)
+    layers = []
+    for i in range(n_layer):
+        kind = i % 4
+        if kind == 0:
+            layers.append(dict(type="delta", mixer=dict(delta), mlp=dict(dense)))
+        elif kind == 1:
+            layers.append(dict(type="parallel", mixer=dict(left=dict(left), right=dict(right), left_scale=1.0,
+                                                           right_scale=1.0), mlp=dict(dense)))
+        elif kind == 2:
+            layers.append(dict(type="attention", mixer=dict(att), mlp=dict(dense)))
+        else:
+            layers.append(dict(type="attention", mixer=dict(att, kv_from=i - 1), mlp=dict(dense)))
+    return dict(architecture="Kemuzen", vocab=vocab, width=width, embedding=dict(scale=float(width) ** 0.5),
+                norm=dict(eps=1e-6), logit_softcap=30.0, token_side=dict(dim=32), layers=layers)
+
+
 def folder_of(raw: dict, seed: int, dtype: torch.dtype) -> str:
     """A folder with seeded random weights of the configuration ``raw`` (made once, in the temporary folder)."""
     from .config.base import architecture_name
@@ -502,7 +532,7 @@ def profile_forward(eng, prompt, batch: int, repeats: int = 3):
 
 def compare_designs(widths=(768, 1024, 1600), n_layer: int = 4, batch: int = 8, context: int = 1024,
                     steps: int = 64, warmup: int = 8, designs=("vadonex", "gpt2")) -> List[dict]:
-    """The ``designs`` (of "mulavik", "vadonex", "gpt2") side by side at equal width, depth, vocabulary and
+    """The ``designs`` (of "kemuzen", "mulavik", "vadonex", "gpt2") side by side at equal width, depth, vocabulary and
     context (random weights, bfloat16): one prompt of ``context - steps - warmup`` tokens in one step, decode at
     ``batch``, and where the time of each goes op by op with every op's fraction of its roofline (measured
     peaks)."""
@@ -513,7 +543,8 @@ def compare_designs(widths=(768, 1024, 1600), n_layer: int = 4, batch: int = 8, 
                     n_layer=n_layer, n_head=width // 64, layer_norm_epsilon=1e-5, activation_function="gelu_new")
         record = {"width": width, "n_layer": n_layer, "batch": batch, "context": context}
         made = {"vadonex": lambda: vadonex_like(width, n_layer, 50257, context), "gpt2": lambda: gpt2,
-                "mulavik": lambda: mulavik_like(width, n_layer, 50257)}
+                "mulavik": lambda: mulavik_like(width, n_layer, 50257),
+                "kemuzen": lambda: kemuzen_like(width, n_layer, 50257)}
         for name in designs:
             raw = made[name]()
             d = folder_of(raw, 1234, torch.bfloat16)

@@ -124,12 +124,14 @@ int nib_attention_decode(int dtype, const void* q, int ldq, const void* cache, f
                          int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int chunk,
                          int n_splits, int* counters, int* status, cudaStream_t stream);
 
-// Tiled tensor-core attention for prompt portions (bfloat16, head sizes 16..128 in steps of 16).
+// Tiled tensor-core attention for prompt portions (bfloat16, head sizes 16..128 in steps of 16), with the options of
+// AttnExtras.
 int nib_attention_prefill_supported(int head_dim);
 int nib_attention_prefill(const void* q, int ldq, const void* cache, void* out, int ldo,
                           const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                           const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
-                          int head_dim, int page_size, int n_pages, float scale, int window, int sink, int* status,
+                          int head_dim, int page_size, int n_pages, float scale, int window, int sink, float softcap,
+                          int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int* status,
                           cudaStream_t stream);
 
 // Loading: src holds [rows, cols] values as a checkpoint stores them (src_dtype 0: 32-bit floats, 1:

@@ -13,6 +13,11 @@
 // and fixes the head size at 64).  Several requests share a launch: the host lists the tiles as
 // (entry, first row within the entry).
 //
+// With EX the kernel also takes the options of AttnExtras (api.h): a soft cap and a distance bias on the scores
+// (the cap by tanh(x) = 1 - 2 / (1 + e^2x) with the hardware's 2^x and reciprocal, relative error about 1e-6), the
+// first `keep_first` keys visible behind the window (their tiles are walked ahead of the window's), and the output
+// times sigmoid(gate[t, h]) and a constant.
+//
 // The warp-level MMA keeps S and P in registers, which the softmax between the two products wants;
 // the head size 64 of this architecture gives the 128-row tcgen05 shapes little to work on.
 #include "api.h"
@@ -54,13 +59,13 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi) {
   return *reinterpret_cast<uint32_t*>(&h);
 }
 
-template <int HD>
+template <int HD, bool EX>
 __global__ void __launch_bounds__(PF_THREADS)
 attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
                          int ldo, const int* __restrict__ block_table, int max_blocks,
                          const int* __restrict__ tiles, const int* __restrict__ entry_start,
                          const int* __restrict__ entry_pos0, int n_head, int n_kv_head, int page_size, int n_pages,
-                         float scale, int window, int sink, int* __restrict__ status) {
+                         float scale, int window, int sink, AttnExtras ex, int* __restrict__ status) {
   pdl_trigger();
   pdl_wait();
   constexpr int LD = HD + 8;               // padded row: ldmatrix reads without bank conflicts
@@ -81,6 +86,11 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
   const int* table = block_table + (size_t)e * max_blocks;
   const int key_lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
   const int tile_first = key_lo / PF_BN, tile_last = pos_last / PF_BN;
+  // keys 0 .. keep - 1 stay visible behind the window: their tiles, those ahead of the window's first, come first
+  const int keep = EX && window > 0 ? ex.keep_first : 0;
+  const int n_kept = min(tile_first, (keep + PF_BN - 1) / PF_BN);
+  const int n_it = n_kept + tile_last - tile_first + 1;
+  auto tile_of = [&](int it) { return it < n_kept ? it : tile_first + it - n_kept; };
 
   // ---- Q tile -> shared memory (rows past the request's end are zeros)
   for (int c = tid; c < PF_BM * CHUNKS; c += PF_THREADS) {
@@ -103,7 +113,7 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
         const int page = table[page_size == 16 ? (j >> 4) : j / page_size];
         if (page < 0 || page >= n_pages) {
           valid = false;
-          if (j >= key_lo) *status = NIB_STATUS_BAD_PAGE;  // pages behind a window may be gone, and are not read
+          if (j >= key_lo || j < keep) *status = NIB_STATUS_BAD_PAGE;  // pages behind a window may be gone, and are not read
         } else {
           const int slot = page_size == 16 ? (j & 15) : j % page_size;
           src = head_base + (size_t)page * 2 * kv_stride + (size_t)slot * HD + piece * 8;
@@ -113,7 +123,7 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
       cp_async16(vs + (buf * PF_BN + r) * LD + piece * 8, src + kv_stride, valid);
     }
   };
-  load_kv(tile_first, 0);
+  load_kv(tile_of(0), 0);
   cp_async_commit();
 
   // accumulators: this thread holds rows (lane / 4) and (lane / 4 + 8) of its warp's 16
@@ -127,15 +137,19 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
   const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
   const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
   uint32_t qf[HD / 16][4];
-  const float scale2 = scale * 1.4426950408889634f;
+  constexpr float LOG2E = 1.4426950408889634f;
+  const float scale2 = EX ? 1.0f : scale * LOG2E;   // (with EX the scores are brought to their final form first)
+  const float slope2 = EX && ex.slopes ? ex.slopes[h] * LOG2E : 0.0f;
+  const float cap2 = EX ? ex.softcap * LOG2E : 0.0f, cap_in = EX && ex.softcap > 0.0f ? 2.0f * LOG2E * scale / ex.softcap : 0.0f;
 
-  for (int tile = tile_first; tile <= tile_last; ++tile) {
-    const int buf = (tile - tile_first) & 1;
-    if (tile < tile_last) load_kv(tile + 1, buf ^ 1);
+  for (int it = 0; it < n_it; ++it) {
+    const int tile = tile_of(it);
+    const int buf = it & 1;
+    if (it + 1 < n_it) load_kv(tile_of(it + 1), buf ^ 1);
     cp_async_commit();
     cp_async_wait<1>();          // everything but the newest group has landed: Q and this tile
     __syncthreads();
-    if (tile == tile_first) {
+    if (it == 0) {
 #pragma unroll
       for (int kk = 0; kk < HD / 16; ++kk)
         ldmatrix_x4(qf[kk], qs + (rg * 16 + (lane & 7) + 8 * ((lane >> 3) & 1)) * LD + kk * 16 + 8 * (lane >> 4));
@@ -162,15 +176,29 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
     const int wp0 = pos_first + rg * 16, wp1 = wp0 + 15;     // positions of the warp's rows
     const int wj0 = tile * PF_BN + kh * PF_WN;               // the warp's first key of the tile
     const bool edge = wj0 + PF_WN - 1 > wp0 || (window > 0 && wj0 < wp1 - window + 1);
+    const int j_base = wj0 + (lane & 3) * 2;
+    if (EX) {
+      // the score in its final form, times log2(e): scale, cap, distance bias
+#pragma unroll
+      for (int i = 0; i < PF_WN / 8; ++i) {
+#pragma unroll
+        for (int c = 0; c < 4; ++c) {
+          float t = s[i][c];
+          if (cap_in > 0.0f) t = cap2 - __fdividef(2.0f * cap2, 1.0f + pow2(t * cap_in));
+          else t *= scale * LOG2E;
+          const int j = j_base + i * 8 + (c & 1);
+          s[i][c] = t - slope2 * (float)((c < 2 ? p0 : p1) - j);
+        }
+      }
+    }
     if (edge) {
-      const int j_base = wj0 + (lane & 3) * 2;
 #pragma unroll
       for (int i = 0; i < PF_WN / 8; ++i) {
 #pragma unroll
         for (int c = 0; c < 2; ++c) {
           const int j = j_base + i * 8 + c;
-          if (!(j <= p0 && j >= lo0)) s[i][c] = -INFINITY;
-          if (!(j <= p1 && j >= lo1)) s[i][2 + c] = -INFINITY;
+          if (!(j <= p0 && (j >= lo0 || j < keep))) s[i][c] = -INFINITY;
+          if (!(j <= p1 && (j >= lo1 || j < keep))) s[i][2 + c] = -INFINITY;
         }
       }
     }
@@ -266,7 +294,15 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
   }
 
   // ---- normalise and store
-  const float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+  float i0 = l0 > 0.0f ? 1.0f / l0 : 0.0f, i1 = l1 > 0.0f ? 1.0f / l1 : 0.0f;
+  if (EX) {
+    i0 *= ex.out_scale;
+    i1 *= ex.out_scale;
+    if (ex.gate) {
+      if (r0 < n_rows) i0 *= 1.0f / (1.0f + __expf(-ex.gate[(size_t)(row0 + r0) * ex.ldg + h]));
+      if (r1 < n_rows) i1 *= 1.0f / (1.0f + __expf(-ex.gate[(size_t)(row0 + r1) * ex.ldg + h]));
+    }
+  }
 #pragma unroll
   for (int i = 0; i < HD / 8; ++i) {
     const int d = h * HD + i * 8 + (lane & 3) * 2;
@@ -277,23 +313,23 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
   }
 }
 
-template <int HD>
+template <int HD, bool EX>
 static int launch_prefill(const void* q, int ldq, const void* cache, void* out, int ldo, const int* block_table,
                           int max_blocks, const int* tiles, int n_tiles, const int* entry_start,
                           const int* entry_pos0, int n_head, int n_kv_head, int page_size, int n_pages, float scale,
-                          int window, int sink, int* status, cudaStream_t stream) {
+                          int window, int sink, const AttnExtras& ex, int* status, cudaStream_t stream) {
   const size_t smem = (size_t)(PF_BM + 4 * PF_BN) * (HD + 8) * sizeof(bf16);
   static bool attr_set = false;
   if (!attr_set && smem > 48 * 1024) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel<HD, EX>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)smem);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
   dim3 grid(n_head, n_tiles);
-  launch_pdl(attention_prefill_kernel<HD>, dim3(grid), dim3(PF_THREADS), smem, stream, 
+  launch_pdl(attention_prefill_kernel<HD, EX>, dim3(grid), dim3(PF_THREADS), smem, stream, 
       (const bf16*)q, ldq, (const bf16*)cache, (bf16*)out, ldo, block_table, max_blocks, tiles, entry_start,
-      entry_pos0, n_head, n_kv_head, page_size, n_pages, scale, window, sink, status);
+      entry_pos0, n_head, n_kv_head, page_size, n_pages, scale, window, sink, ex, status);
   NIB_LAUNCH_CHECK();
 }
 
@@ -312,16 +348,24 @@ extern "C" int nib_attention_prefill(const void* q, int ldq, const void* cache, 
                                      const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                                      const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
                                      int head_dim, int page_size, int n_pages, float scale, int window,
-                                     int sink, int* status, cudaStream_t stream) {
+                                     int sink, float softcap, int keep_first, const float* slopes,
+                                     const float* gate, int ldg, float out_scale, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale};
+  const bool plain = !(softcap > 0.0f) && (keep_first <= 0 || window <= 0) && !slopes && !gate && out_scale == 1.0f;
+  if (softcap < 0.0f || keep_first < 0) return NIB_ERR_BAD_ARGUMENT;
   if (!nib_attention_prefill_supported(head_dim)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f)) return NIB_ERR_BAD_ARGUMENT;
   if ((ldq & 7) || ((uintptr_t)q & 15) || (ldo & 1) || ((uintptr_t)out & 3)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_tiles > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
 #define NIB_PF_CASE(D)                                                                                         \
   case D:                                                                                                      \
-    return launch_prefill<D>(q, ldq, cache, out, ldo, block_table, max_blocks, tiles, n_tiles, entry_start,    \
-                             entry_pos0, n_head, n_kv_head, page_size, n_pages, scale, window, sink, status, stream);
+    return plain ? launch_prefill<D, false>(q, ldq, cache, out, ldo, block_table, max_blocks, tiles, n_tiles,  \
+                                            entry_start, entry_pos0, n_head, n_kv_head, page_size, n_pages,    \
+                                            scale, window, sink, ex, status, stream)                           \
+                 : launch_prefill<D, true>(q, ldq, cache, out, ldo, block_table, max_blocks, tiles, n_tiles,   \
+                                           entry_start, entry_pos0, n_head, n_kv_head, page_size, n_pages,     \
+                                           scale, window, sink, ex, status, stream);
   switch (head_dim) {
     NIB_PF_CASE(16) NIB_PF_CASE(32) NIB_PF_CASE(48) NIB_PF_CASE(64) NIB_PF_CASE(80) NIB_PF_CASE(96)
     NIB_PF_CASE(112) NIB_PF_CASE(128)

@@ -70,7 +70,8 @@ _SIGNATURES = {
                                  _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
     "nib_attention_prefill_supported": [_c_int],
     "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
-                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
+                              _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_float, _c_int,
+                              _c_ptr, _c_ptr, _c_int, _c_float, _c_ptr, _c_ptr],
     "nib_convert": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_ptr],
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
@@ -836,7 +837,8 @@ def attention_prefill_tc(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                       tiles: torch.Tensor, n_tiles: int, entry_start: torch.Tensor, entry_pos0: torch.Tensor,
-                      n_head: int, scale: float, window: int, status: torch.Tensor, sink: bool = False) -> None:
+                      n_head: int, scale: float, window: int, status: torch.Tensor, sink: bool = False,
+                      extras: Optional[AttnExtras] = None) -> None:
     """Tiled tensor-core attention for prompt portions: ``tiles`` holds (entry, first row within the
     entry) pairs of 64 rows each."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
@@ -845,8 +847,8 @@ def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, b
     _check(library().nib_attention_prefill(_ptr(q), q.stride(0), _ptr(cache), _ptr(out), out.stride(0),
                                            _ptr(block_table), block_table.shape[1], _ptr(tiles), n_tiles,
                                            _ptr(entry_start), _ptr(entry_pos0), n_head, n_kv_head, head_dim,
-                                           page_size, n_pages, float(scale), int(window), int(sink), _ptr(status),
-                                           _stream()), "attention_prefill")
+                                           page_size, n_pages, float(scale), int(window), int(sink),
+                                           *(extras or _NO_EXTRAS).args(), _ptr(status), _stream()), "attention_prefill")
 
 
 def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor, ctx,
@@ -886,10 +888,10 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
                 and out.data_ptr() % 16 == 0:
             attention_prefill_tc(q, cache, out, block_table, plan.wide_tiles, plan.n_wide_tiles, ctx.entry_start,
                                  ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status, sink=sink)
-        elif plain and q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
+        elif q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
             attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
-                              n_head, scale, window, ctx.status, sink=sink)
+                              n_head, scale, window, ctx.status, sink=sink, extras=extras)
         else:
             # (portions alone: all of the step's rows, those of no request among them, which the kernel leaves out;
             # the launch then depends on the step's shape only, as a graph needs it)
