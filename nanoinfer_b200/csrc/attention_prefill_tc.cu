@@ -17,6 +17,11 @@
 // (crates/core/src/kernels/reference.rs:109-142); tiling after the reference's attn_prefill_flash
 // (crates/metal/src/shaders/attn.metal:100-218).
 //
+// With EX the kernel takes the options of AttnExtras (api.h).  The softmax threads bring every score to its final
+// form first (scale, cap, distance bias, times log2(e); the cap by tanh(x) = 1 - 2 / (1 + e^2x) with the hardware's
+// 2^x and division, relative error about 1e-6); the tiles of the first `keep_first` keys, which stay visible behind
+// the window, are walked ahead of the window's; the output is multiplied by sigmoid(gate[t, h]) and a constant.
+//
 // Every wait on a barrier is bounded: a wait that runs out sets the block's abort flag and the
 // device status word, every role leaves its loop, tensor memory is freed, and the kernel returns.
 #include "api.h"
@@ -44,6 +49,7 @@ struct AtParams {
   bf16* out;
   int ldo;
   int* status;
+  AttnExtras ex;
 };
 
 __device__ __forceinline__ void tmem_ld32(uint32_t taddr, float* v) {
@@ -102,7 +108,7 @@ struct AtShape {
   static constexpr size_t SMEM = 16384 + 2 * AT_STAGES * KV_STAGE + AT_NBUF * P_BYTES + 1024;
 };
 
-template <int AT_BN>
+template <int AT_BN, bool EX>
 __global__ void __launch_bounds__(AT_THREADS, AT_BN == 64 ? 2 : 1)
 attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __grid_constant__ CUtensorMap map_kv,
                             const AtParams prm) {
@@ -134,7 +140,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int window = prm.window;
   const int key_lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
   const int tile_first = key_lo / AT_BN, tile_last = pos_last / AT_BN;
-  const int n_it = tile_last - tile_first + 1;
+  // keys 0 .. keep - 1 stay visible behind the window: their tiles, those ahead of the window's first, come first
+  const int keep = EX && window > 0 ? prm.ex.keep_first : 0;
+  const int n_kept = min(tile_first, (keep + AT_BN - 1) / AT_BN);
+  const int n_it = n_kept + tile_last - tile_first + 1;
+  auto tile_of = [&](int it) { return it < n_kept ? it : tile_first + it - n_kept; };
 
   if (threadIdx.x == 0) {
     abort_sh = 0;
@@ -176,8 +186,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     // request that is there (finite values, weight zero)
     auto unit_row = [&](int it) -> int {
       if (!active || it >= n_it) return -1;
-      int j = (tile_first + it) * AT_BN + u * AT_UNIT;
-      j = max(min(j, pos_last), key_lo) / AT_UNIT * AT_UNIT;
+      int j = min(tile_of(it) * AT_BN + u * AT_UNIT, pos_last) / AT_UNIT * AT_UNIT;
+      // (a unit with no visible key, behind the window and past the kept keys, may lie on a page that is gone)
+      if (j + AT_UNIT - 1 < key_lo && j >= keep) j = (it < n_kept ? keep - 1 : key_lo) / AT_UNIT * AT_UNIT;
       const int page = table[j / prm.page_size];
       if (page < 0 || page >= prm.n_pages) {
         *prm.status = NIB_STATUS_BAD_PAGE;
@@ -252,7 +263,12 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int p = pos_first + r;
     const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
     const int wp0 = pos_first + quarter * 32, wp1 = wp0 + 31;   // positions of the warp's rows
-    const float scale2 = prm.scale * 1.4426950408889634f;
+    constexpr float LOG2E = 1.4426950408889634f;
+    const float scale2 = EX ? 1.0f : prm.scale * LOG2E;   // (with EX the scores are brought to their final form first)
+    const float slope2 = EX && prm.ex.slopes ? prm.ex.slopes[h] * LOG2E : 0.0f;
+    const float cap2 = EX ? prm.ex.softcap * LOG2E : 0.0f;
+    const float cap_in = EX && prm.ex.softcap > 0.0f ? 2.0f * LOG2E * prm.scale / prm.ex.softcap : 0.0f;
+    const float mul2 = prm.scale * LOG2E;
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
@@ -260,15 +276,26 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       ok = warp_mbar_wait(&s_full[b], (it / AT_NBUF) & 1, abort_flag, lane);
       if (!ok) break;
       tc_fence_after();
-      const int j0 = (tile_first + it) * AT_BN;
+      const int j0 = tile_of(it) * AT_BN;
       const bool edge = j0 + AT_BN - 1 > wp0 || (window > 0 && j0 < wp1 - window + 1);   // only these tiles need the mask
       float v[AT_BN];
 #pragma unroll
       for (int c = 0; c < AT_BN / 32; ++c) tmem_ld32(lane_addr + (uint32_t)(b * AT_BN + c * 32), v + c * 32);
+      if (EX) {
+        const float far = (float)(p - j0);
+        if (cap_in > 0.0f) {
+#pragma unroll
+          for (int i = 0; i < AT_BN; ++i)
+            v[i] = cap2 - __fdividef(2.0f * cap2, 1.0f + at_pow2(v[i] * cap_in)) - slope2 * (far - (float)i);
+        } else {
+#pragma unroll
+          for (int i = 0; i < AT_BN; ++i) v[i] = fmaf(v[i], mul2, -slope2 * (far - (float)i));
+        }
+      }
       if (edge) {
 #pragma unroll
         for (int i = 0; i < AT_BN; ++i)
-          if (!(j0 + i <= p && j0 + i >= lo)) v[i] = -INFINITY;
+          if (!(j0 + i <= p && (j0 + i >= lo || j0 + i < keep))) v[i] = -INFINITY;
       }
       float mx4[4] = {-INFINITY, -INFINITY, -INFINITY, -INFINITY};   // four chains, not one of 64 links
 #pragma unroll
@@ -334,7 +361,11 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok) {
       tc_fence_after();
       if (prm.sink && m != -INFINITY) l += at_pow2(-m);
-      const float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      float inv = l > 0.0f ? 1.0f / l : 0.0f;
+      if (EX) {
+        inv *= prm.ex.out_scale;
+        if (prm.ex.gate && r < n_rows) inv *= 1.0f / (1.0f + __expf(-prm.ex.gate[(size_t)(row0 + r) * prm.ex.ldg + h]));
+      }
       bf16* dst = prm.out + (size_t)(row0 + r) * prm.ldo + h * AT_HD;
 #pragma unroll 1
       for (int c = 0; c < AT_HD / 32; ++c) {
@@ -375,8 +406,11 @@ extern "C" int nib_attention_prefill_tc(const void* q, int ldq, int T, const voi
                                         const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                                         const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
                                         int head_dim, int page_size, int n_pages, float scale, int window,
-                                        int sink, int* status, cudaStream_t stream) {
+                                        int sink, float softcap, int keep_first, const float* slopes, const float* gate,
+                                        int ldg, float out_scale, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
+  if (softcap < 0.0f || keep_first < 0) return NIB_ERR_BAD_ARGUMENT;
+  const bool plain = !(softcap > 0.0f) && (keep_first <= 0 || window <= 0) && !slopes && !gate && out_scale == 1.0f;
   if (!nib_attention_prefill_tc_supported(head_dim, page_size)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f) || T <= 0) return NIB_ERR_BAD_ARGUMENT;
   if ((ldq & 7) || ((uintptr_t)q & 15) || (ldo & 7) || ((uintptr_t)out & 15) || ((uintptr_t)cache & 15))
@@ -392,17 +426,25 @@ extern "C" int nib_attention_prefill_tc(const void* q, int ldq, int T, const voi
   prm.entry_start = entry_start; prm.entry_pos0 = entry_pos0;
   prm.n_head = n_head; prm.n_kv_head = n_kv_head; prm.page_size = page_size; prm.n_pages = n_pages;
   prm.scale = scale; prm.window = window; prm.sink = sink; prm.out = (bf16*)out; prm.ldo = ldo; prm.status = status;
+  prm.ex = AttnExtras{softcap, keep_first, slopes, gate, ldg, out_scale};
   // 128 keys a tile, one block an SM: measured a little faster than 64 keys a tile and two blocks
   constexpr int BN = 128;
   static bool attr_set = false;
   if (!attr_set) {
-    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+    cudaError_t e = cudaFuncSetAttribute(attention_prefill_tc_kernel<BN, false>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                          (int)AtShape<BN>::SMEM);
+    if (e == cudaSuccess)
+      e = cudaFuncSetAttribute(attention_prefill_tc_kernel<BN, true>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                               (int)AtShape<BN>::SMEM);
     if (e != cudaSuccess) return (int)e;
     attr_set = true;
   }
-  launch_pdl(attention_prefill_tc_kernel<BN>, dim3(n_head, n_tiles), dim3(AT_THREADS), AtShape<BN>::SMEM, stream, map_q,
-             map_kv, prm);
+  if (plain)
+    launch_pdl(attention_prefill_tc_kernel<BN, false>, dim3(n_head, n_tiles), dim3(AT_THREADS), AtShape<BN>::SMEM, stream,
+               map_q, map_kv, prm);
+  else
+    launch_pdl(attention_prefill_tc_kernel<BN, true>, dim3(n_head, n_tiles), dim3(AT_THREADS), AtShape<BN>::SMEM, stream,
+               map_q, map_kv, prm);
   NIB_LAUNCH_CHECK();
 }
 

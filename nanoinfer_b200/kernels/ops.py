@@ -56,7 +56,8 @@ _SIGNATURES = {
                           _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_attention_prefill_tc_supported": [_c_int, _c_int],
     "nib_attention_prefill_tc": [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr,
-                                 _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr],
+                                 _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_float, _c_int,
+                                 _c_ptr, _c_ptr, _c_int, _c_float, _c_ptr, _c_ptr],
     "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_float, _c_int,
                            _c_ptr, _c_ptr, _c_int, _c_float, _c_ptr, _c_ptr],
@@ -820,7 +821,7 @@ def attention_decode(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, bl
 def attention_prefill_tc(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
                          tiles: torch.Tensor, n_tiles: int, entry_start: torch.Tensor, entry_pos0: torch.Tensor,
                          n_rows: int, n_head: int, scale: float, window: int, status: torch.Tensor,
-                         sink: bool = False) -> None:
+                         sink: bool = False, extras: Optional[AttnExtras] = None) -> None:
     """tcgen05 attention for prompt portions (bfloat16, head size 64): ``tiles`` holds (entry, first
     row within the entry) pairs of 128 rows each; ``q`` holds the step's ``n_rows`` rows."""
     n_pages, _, n_kv_head, page_size, head_dim = cache.shape
@@ -831,8 +832,9 @@ def attention_prefill_tc(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor
     _check(library().nib_attention_prefill_tc(_ptr(q), q.stride(0), n_rows, _ptr(cache), _ptr(out), out.stride(0),
                                               _ptr(block_table), block_table.shape[1], _ptr(tiles), n_tiles,
                                               _ptr(entry_start), _ptr(entry_pos0), n_head, n_kv_head, head_dim,
-                                              page_size, n_pages, float(scale), int(window), int(sink), _ptr(status),
-                                              _stream()), "attention_prefill_tc")
+                                              page_size, n_pages, float(scale), int(window), int(sink),
+                                              *(extras or _NO_EXTRAS).args(), _ptr(status), _stream()),
+           "attention_prefill_tc")
 
 
 def attention_prefill(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_table: torch.Tensor,
@@ -855,7 +857,7 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
               n_head: int, scale: float, window: int, plan, sink: bool = False,
               extras: Optional[AttnExtras] = None) -> None:
     """Causal attention of the step's rows over one cache layer.  ``extras``: options on the scores and the output
-    (``AttnExtras``); the kernels that take them are the general one and the streaming split-KV one.  ``sink``: the softmax's denominator has
+    (``AttnExtras``); the kernels that take them are the general one, the two of prompt portions and the streaming split-KV one.  ``sink``: the softmax's denominator has
     one more term, exp(0) (a key of score 0 that has no value; every kernel adds it where it divides).
     ``ctx`` is the step's StepContext, ``plan`` says which rows are single decoded tokens and how the
     prompt portions are cut into tiles (``parts.attention.AttentionPlan``).  Single decoded tokens go to the split-KV kernel;
@@ -883,11 +885,11 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
         if traced:
             _note_attention(plan.n_prefill_rows, plan.prefill_keys, plan.prefill_kv_rows, n_head, n_kv_head, head_dim,
                             q.element_size())
-        if plain and q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
+        if q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 \
                 and out.data_ptr() % 16 == 0:
             attention_prefill_tc(q, cache, out, block_table, plan.wide_tiles, plan.n_wide_tiles, ctx.entry_start,
-                                 ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status, sink=sink)
+                                 ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status, sink=sink, extras=extras)
         elif q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
             attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,

@@ -397,6 +397,59 @@ def test_attention_kernels_with_options_on_scores_and_output(name, hd, n_head, n
     assert float((plain - with_options).abs().max()) > 20 * tol
 
 
+LONG_OPTION_SETS = {
+    "kept tokens a tile or more behind the window": dict(window=70, keep_first=5, softcap=6.0),
+    "more kept tokens than a tile holds": dict(window=40, keep_first=150),
+    "kept tokens that end in the window's first tile": dict(window=200, keep_first=140, softcap=11.0),
+    "a distance bias, a gate and a constant behind a window": dict(window=260, slopes=True, gate=True, out_scale=0.6),
+    "a cap and a distance bias over all keys": dict(softcap=3.0, slopes=True),
+}
+
+
+@pytest.mark.parametrize("hd,n_head,n_kv_head", [(64, 4, 2), (64, 3, 1), (32, 2, 2), (128, 2, 1), (48, 4, 4)])
+@pytest.mark.parametrize("name", list(LONG_OPTION_SETS))
+def test_prompt_kernels_with_options_over_many_tiles(name, hd, n_head, n_kv_head):
+    """Long portions in bfloat16, so that the tiled tensor-core kernels of prompts (the tcgen05 one at head size 64,
+    the warp-MMA one elsewhere) walk several tiles of keys, those of the kept tokens ahead of the window's, with rows
+    that start anywhere in a tile and pages in any order."""
+    from nanoinfer_b200.kernels import ops
+    from nanoinfer_b200.parts.attention import AttentionPlan
+
+    o = dict(LONG_OPTION_SETS[name])
+    dt, page, scale = torch.bfloat16, 16, 1.3 / math.sqrt(hd)
+    slopes = torch.tensor([2.0 ** (-8.0 * (h + 1) / n_head) for h in range(n_head)]) if o.pop("slopes", False) else None
+    want_gate = o.pop("gate", False)
+    window = o.get("window", 0)
+    lengths, q_rows = [700, 333, 390, 131], [300, 290, 3, 130]
+    cache, table, ks, vs, qs = _paged(dt, n_head, n_kv_head, hd, page, lengths, q_rows, seed=hd + n_head)
+    positions = [p for n, r in zip(lengths, q_rows) for p in range(n - r, n)]
+    ctx = step_ctx(q_rows, positions)
+    T = ctx.n_rows
+    gate = torch.randn(T, n_head + 1) * 2 if want_gate else None
+    want, r0 = [], 0
+    for qq, k, v, n, r in zip(qs, ks, vs, lengths, q_rows):
+        want.append(_option_attention(qq, k, v, scale, n - r, slopes=slopes, gate=gate[r0:r0 + r] if want_gate else None, **o))
+        r0 += r
+    want = torch.cat(want)
+    q = torch.cat(qs).view(-1, n_head * hd).to(dt).to(DEV)
+    ex = ops.AttnExtras(o.get("softcap", 0.0), o.get("keep_first", 0), slopes.to(DEV) if slopes is not None else None,
+                        gate.to(DEV)[:, :n_head] if want_gate else None, o.get("out_scale", 1.0))
+    cache_d = cache.to(dt).to(DEV)
+    if window:
+        # pages that hold nothing visible to any row of the step are gone: the kernels must not need them
+        for e, (n, r) in enumerate(zip(lengths, q_rows)):
+            for b in range(-(-n // page)):
+                if (b + 1) * page <= n - r - window + 1 and b * page >= o.get("keep_first", 0):
+                    cache_d[int(table[e, b])] = float("nan")
+                    table[e, b] = -1
+    out = torch.full_like(q, 7.0)
+    plan = AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0, device=torch.device(DEV))
+    ops.attention(q, cache_d, out, table.to(DEV), ctx, n_head, scale, window, plan, extras=ex)
+    assert int(ctx.status.item()) == 0
+    diff = (out.double().cpu().view(want.shape) - want).abs()
+    assert float(diff.max()) < 2e-2, f"{name}: {float(diff.max()):.3e} at row {int(diff.amax((1, 2)).argmax())}"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("rows", [1, 40])
 def test_one_matching_key_at_the_edges_of_the_window_and_of_the_kept_tokens(rows, dtype):
