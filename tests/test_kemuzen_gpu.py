@@ -673,6 +673,24 @@ def test_long_decoding_behind_windows_gives_pages_back_but_not_the_first(dtype, 
     assert h.runner.graph_replays > 300
 
 
+@pytest.mark.parametrize("dtype", ["bfloat16", "float32"])
+def test_long_prompts_through_the_tiled_prompt_kernels(dtype, tmp_path):
+    """Heads of 64 (the tcgen05 prompt kernel in bfloat16) and of 128 and 32 (the warp-MMA one) over prompts of
+    several tiles of keys: windows that end in the middle of a tile, kept tokens a tile or more behind them, a layer
+    that reads another's cache with a narrower window and more kept tokens, a distance bias over hundreds of keys;
+    whole, in portions that start anywhere, and with the last tokens one by one."""
+    layers = [attention_layer(heads=4, kv_heads=2, dim=64, vdim=64, softcap=15.0, window=150, keep_first=5, mlp=dense(40)),
+              parallel_layer(heads=2, kv_heads=1, dim=64, vdim=32, window=210, r_heads=2, r_vdim=16, state=16),
+              attention_layer(heads=4, kv_heads=2, dim=64, vdim=64, softcap=None, window=70, keep_first=140, kv_from=0),
+              attention_layer(heads=2, kv_heads=1, dim=128, vdim=64, softcap=8.0, window=129, keep_first=1),
+              parallel_layer(heads=3, kv_heads=3, dim=32, vdim=32, window=None, r_heads=1, r_vdim=8, state=8, conv=2)]
+    h = Harness(config(layers, vocab=150, width=64), tmp_path, dtype, max_tokens=1216, slots=2, max_rows=640, seed=5)
+    tokens = toks(150, 590, 77)
+    h.check(h.alone(tokens, [590]), tokens, "whole")
+    h.check(h.alone(tokens, [333, 2, 131, 100] + [1] * 24), tokens, "in portions")
+    assert h.cache.pages_used() == [0] * len(h.cache.groups)
+
+
 def test_a_token_far_back_shows_through_the_state_and_through_the_kept_tokens(tmp_path):
     """Recurrences whose rates let them remember for hundreds of tokens, and an attention that keeps its first
     token behind a short window: two prompts that differ in their first token only still differ 150 tokens on, and
