@@ -19,7 +19,12 @@
 //   slopes:       one number per query head, s <- s - slopes[h] (query position - key position);
 //   keep_first:   with a window, keys 0 .. keep_first - 1 stay visible behind it;
 //   gate:         head h's output of row t is multiplied by sigmoid(gate[t * ldg + h]);
-//   out_scale:    and by this constant.
+//   out_scale:    and by this constant;
+//   span > 0:     position i sees key j only if floor(i / span) == floor(j / span) (spans count from position 0 of
+//                 the sequence);
+//   head_scale:   one number per query head that multiplies the scale (a temperature);
+//   sinks:        with `sink` set, one number per query head: the denominator's extra term is exp(sinks[h]) instead
+//                 of exp(0).
 struct AttnExtras {
   float softcap;
   int keep_first;
@@ -27,6 +32,9 @@ struct AttnExtras {
   const float* gate;
   int ldg;
   float out_scale;
+  int span;
+  const float* head_scale;
+  const float* sinks;
 };
 
 #ifdef __cplusplus
@@ -103,7 +111,7 @@ int nib_attention_simt(int dtype, const void* q, int ldq, const void* cache, voi
                        const int* block_table, int max_blocks, const int* rows, const int* row_entry,
                        const int* positions, int T, int n_head, int n_kv_head, int head_dim,
                        int page_size, int n_pages, float scale, int window, int sink, float softcap,
-                       int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int* status,
+                       int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int* status,
                        cudaStream_t stream);
 
 // tcgen05 attention for prompt portions (bfloat16, head size 64, page size a multiple of 16): tiles of
@@ -114,7 +122,7 @@ int nib_attention_prefill_tc(const void* q, int ldq, int T, const void* cache, v
                              const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                              const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head, int head_dim,
                              int page_size, int n_pages, float scale, int window, int sink, float softcap, int keep_first,
-                             const float* slopes, const float* gate, int ldg, float out_scale, int* status,
+                             const float* slopes, const float* gate, int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int* status,
                              cudaStream_t stream);
 
 // Split-KV attention for single decoded tokens (float32 or bfloat16, head sizes up to 128 in steps
@@ -124,7 +132,7 @@ int nib_attention_decode(int dtype, const void* q, int ldq, const void* cache, f
                          int ldo, const int* block_table, int max_blocks, const int* rows,
                          const int* row_entry, const int* positions, int n_rows, int n_head, int n_kv_head,
                          int head_dim, int page_size, int n_pages, float scale, int window, int sink, float softcap,
-                         int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int chunk,
+                         int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int chunk,
                          int n_splits, int* counters, int* status, cudaStream_t stream);
 
 // Tiled tensor-core attention for prompt portions (bfloat16, head sizes 16..128 in steps of 16), with the options of
@@ -134,7 +142,7 @@ int nib_attention_prefill(const void* q, int ldq, const void* cache, void* out, 
                           const int* block_table, int max_blocks, const int* tiles, int n_tiles,
                           const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
                           int head_dim, int page_size, int n_pages, float scale, int window, int sink, float softcap,
-                          int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int* status,
+                          int keep_first, const float* slopes, const float* gate, int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int* status,
                           cudaStream_t stream);
 
 // Loading: src holds [rows, cols] values as a checkpoint stores them (src_dtype 0: 32-bit floats, 1:
@@ -218,15 +226,18 @@ int nib_delta_rule(int dtype, float* proj, int ld, int r_off, int k_off, int v_o
                    int dim, float eps, void* out, int ldo, float* unit, cudaStream_t stream);
 
 // ---- a routed feed-forward (moe.cu)
-// score 0: softmax over all experts; 1: the sigmoids of the chosen experts' logits.
+// score 0: softmax over all experts; 1: the sigmoids of the chosen experts' logits.  choice_bias (may be null): one
+// number per expert added to the score for the choice only.  The experts n_real .. n_expert - 1 have no matrices:
+// a row that chooses one gets its own input times the score added to x [T, C] here, and the id -1.
 int nib_moe_route(int dtype, const void* h, int ldh, const void* w_router, int T, int C, int n_expert, int top,
-                  int renorm, int score, int* ids, float* weights, cudaStream_t stream);
+                  int renorm, int score, const float* choice_bias, int n_real, float* x, int* ids, float* weights,
+                  cudaStream_t stream);
 // gated: w_up [experts, 2F, C], rows 2f and 2f + 1 the gate and the value of output f; inner = act(s g) * (s u) with
 // s = in_weights[t * top + k] (null: 1).
 int nib_moe_up(int dtype, const void* h, int ldh, const void* w_up, const int* ids, void* inner, int T, int C,
-               int F, int top, int act, int gated, const float* in_weights, cudaStream_t stream);
+               int F, int top, int act, float act_prm, int gated, const float* in_weights, cudaStream_t stream);
 int nib_moe_gate_scale(int pre_dtype, int dtype, const void* pre, void* inner, const int* ids, const float* weights,
-                       int T, int n_expert, int F, int top, int act, int on_input, cudaStream_t stream);
+                       int T, int n_expert, int F, int top, int act, float act_prm, int on_input, cudaStream_t stream);
 int nib_moe_down(int dtype, const void* inner, const void* w_down, const int* ids, const float* weights, float* x,
                  int T, int C, int F, int top, cudaStream_t stream);
 // inner [T, n_expert * F] in place: expert e's part of row t times the row's weight for e (0 where not chosen).
@@ -237,7 +248,7 @@ int nib_moe_scale(int dtype, void* inner, const int* ids, const float* weights, 
 // out float [T * top, N] (weighted), phase 2 = x[t] += the sum of row t's parts (src = the parts).
 int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src, const void* w, const int* ids,
                     const float* weights, void* out, float* x, int T, int top, int n_expert, int N, int K, int act,
-                    cudaStream_t stream);
+                    float act_prm, cudaStream_t stream);
 
 // Sinusoidal positions added to the 32-bit stream x [T, C]: entry 2i += sin(position * freqs[i]), entry 2i + 1 += cos.
 int nib_add_sinusoid(float* x, const int* positions, const double* freqs, int T, int C, cudaStream_t stream);
@@ -259,7 +270,7 @@ int nib_norm_rope_append(int dtype, const float* proj, int ld, int q_off, int k_
 int nib_short_conv(const float* proj, int ld, int c_off, int Cn, int taps, const float* w, const float* bias,
                    float* state, long long state_stride, const int* row_entry, const int* entry_start,
                    const int* entry_slot, float* out, int ldo, int T, int n_entries, int act, int fused,
-                   cudaStream_t stream);
+                   void* out16, int ld16, cudaStream_t stream);
 int nib_scan_prepare(const float* proj, int ld, int a_off, int w_off, const float* A_log, const float* dt_bias,
                      float* cv, int ldc, int q_off, int k_off, int N, int n_head, int n_kq, int delta, float* coef, int T,
                      cudaStream_t stream);
@@ -271,6 +282,33 @@ int nib_gated_scan(int delta, const float* cv, int ldc, int q_off, int k_off, in
 int nib_gated_norm(int out_dtype, const float* o, int ldo, const float* gate, int ldg, const float* weight, int wlen,
                    int n_groups, int gs, float eps, int gate_first, float out_scale, void* out, int ld_out, int T,
                    cudaStream_t stream);
+
+// ---- rotary positions in the halves layout (rope.cu): value i of a head's first rot_dims values pairs with value
+// i + rot_dims / 2.  nib_wide_norm_rope_append: queries and keys normed over the whole projection (wq [n_head * dim],
+// wk [n_kv_head * dim]; null: no norm), turned, cast, padded to hd and written to q_out and the cache (cache null:
+// queries only); the values are read at v_off as they stand.  nib_rope_halves: in place on 32-bit rows, the keys
+// then times k_mul, and coef[t, h] = (decay[h], 1) where coef is given.
+int nib_wide_norm_rope_append(int dtype, const float* src, int ld, int q_off, int k_off, int v_off, int n_head,
+                              int n_kv_head, int dim, int vdim, int hd, const float* wq, const float* wk, float eps,
+                              int rot_dims, const double* freqs, const int* positions, const int* row_entry, void* q_out,
+                              int ldq, void* cache, const int* block_table, int max_blocks, int page_size, int n_pages,
+                              int T, int* status, cudaStream_t stream);
+int nib_rope_halves(float* rows, int ld, int q_off, int k_off, int n_head, int dim, int rot_dims, const double* freqs,
+                    const int* positions, float k_mul, const float* decay, float* coef, int T, cudaStream_t stream);
+
+// ---- hyper-connections (hyper.cu): S copies of the residual stream, stream_stride floats apart.
+int nib_hyper_enter(int dtype, const float* x, float* streams, long long stream_stride, int S, const float* in_w,
+                    const float* w_next, float eps, void* xn, int T, int C, cudaStream_t stream);
+int nib_hyper_update(int dtype, float* streams, long long stream_stride, int S, float* y, const float* gate, int ldg,
+                     const float* mix, const float* out_w, const float* in_next, const float* w_next, float eps, void* xn,
+                     float* total, int T, int C, cudaStream_t stream);
+
+// ---- the selective scan of Mamba (selective_scan.cu)
+long long nib_selective_scan_state_floats(int inner, int N);
+int nib_selective_scan(int out_dtype, const float* dtp, int ld_dt, const float* x, int ldx, const float* bc, int ldbc,
+                       int b_off, int c_off, const float* z, int ldz, const float* A_log, const float* D, float* state,
+                       long long state_stride, long long s_off, const int* entry_start, const int* entry_slot,
+                       int n_entries, int inner, int N, void* out, int ldo, cudaStream_t stream);
 
 #ifdef __cplusplus
 }

@@ -97,7 +97,11 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
   const int t = rows ? rows[r] : r;
   const int pos = positions[t];
   const int* table = block_table + (size_t)row_entry[t] * max_blocks;
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (ex.span > 0) lo = max(lo, pos - pos % ex.span);   // only the keys of the position's own span
+  if (ex.head_scale) scale *= ex.head_scale[blockIdx.y];
+  // the sink's term of the denominator in the power-of-two scale (exp(0) unless the heads have logits of their own)
+  const float sink2 = ex.sinks ? ex.sinks[blockIdx.y] * 1.4426950408889634f : 0.0f;
   const int k_begin = lo + split * chunk;
   const int k_end = min(pos + 1, k_begin + chunk);  // exclusive
   const int hk = h / (n_head / n_kv_head);
@@ -248,7 +252,7 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
   for (int w = 0; w < ALL_GROUPS; ++w) L += (gm[w] == -INFINITY) ? 0.0f : gl[w] * pow2<T>(gm[w] - M);
   // a sink (one more term in the denominator: a key of score 0 without a value) counts once, where the row's
   // weights are divided
-  const float L1 = (sink && n_splits == 1) ? L + pow2<T>(-M) : L;
+  const float L1 = (sink && n_splits == 1) ? L + pow2<T>(sink2 - M) : L;
   const float mul1 = n_splits == 1 ? ex.out_scale * (ex.gate ? 1.0f / (1.0f + expf(-ex.gate[(size_t)t * ex.ldg + h])) : 1.0f) : 1.0f;
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
@@ -300,7 +304,7 @@ attention_decode_kernel(const T* q, int ldq, const T* cache, float* part_o,
     const float ls = part_ml[2 * (base + sp) + 1];
     if (ls > 0.0f) Lx += ls * pow2<T>(part_ml[2 * (base + sp)] - Mx);
   }
-  if (sink) Lx += pow2<T>(-Mx);
+  if (sink) Lx += pow2<T>(sink2 - Mx);
   const float mulx = ex.out_scale * (ex.gate ? 1.0f / (1.0f + expf(-ex.gate[(size_t)t * ex.ldg + h])) : 1.0f);
   for (int d = threadIdx.x; d < head_dim; d += blockDim.x) {
     float acc = 0.0f;
@@ -357,10 +361,10 @@ extern "C" int nib_attention_decode(int dtype, const void* q, int ldq, const voi
                                     const int* row_entry, const int* positions, int n_rows, int n_head,
                                     int n_kv_head, int head_dim, int page_size, int n_pages, float scale,
                                     int window, int sink, float softcap, int keep_first, const float* slopes,
-                                    const float* gate, int ldg, float out_scale, int chunk, int n_splits,
+                                    const float* gate, int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int chunk, int n_splits,
                                     int* counters, int* status, cudaStream_t stream) {
   if (n_rows <= 0) return 0;
-  const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale};
+  const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale, span, head_scale, sinks};
   if (head_dim <= 0 || head_dim > DEC_MAX_HD || (head_dim & 7)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (page_size % 16 != 0 || chunk <= 0 || chunk % 16 != 0 || n_splits <= 0) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
@@ -436,5 +440,5 @@ extern "C" int nib_attention_decode_static(int dtype, const void* q, int ldq, co
   if (e != cudaSuccess) return (int)e;
   return nib_attention_decode(dtype, q, ldq, cache, scratch, out, ldo, block_table, max_blocks, rows, row_entry,
                               positions, n_rows, n_head, n_kv_head, head_dim, page_size, n_pages, scale, window,
-                              0, 0.0f, 0, nullptr, nullptr, 0, 1.0f, chunk, n_splits, counters, status, stream);
+                              0, 0.0f, 0, nullptr, nullptr, 0, 1.0f, 0, nullptr, nullptr, chunk, n_splits, counters, status, stream);
 }

@@ -349,11 +349,12 @@ extern "C" int nib_attention_prefill(const void* q, int ldq, const void* cache, 
                                      const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
                                      int head_dim, int page_size, int n_pages, float scale, int window,
                                      int sink, float softcap, int keep_first, const float* slopes,
-                                     const float* gate, int ldg, float out_scale, int* status, cudaStream_t stream) {
+                                     const float* gate, int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
-  const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale};
+  const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale, span, head_scale, sinks};
   const bool plain = !(softcap > 0.0f) && (keep_first <= 0 || window <= 0) && !slopes && !gate && out_scale == 1.0f;
   if (softcap < 0.0f || keep_first < 0) return NIB_ERR_BAD_ARGUMENT;
+  if (span > 0 || head_scale != nullptr || sinks != nullptr) return NIB_ERR_UNSUPPORTED_SIZE;
   if (!nib_attention_prefill_supported(head_dim)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f)) return NIB_ERR_BAD_ARGUMENT;
   if ((ldq & 7) || ((uintptr_t)q & 15) || (ldo & 1) || ((uintptr_t)out & 3)) return NIB_ERR_UNSUPPORTED_SIZE;

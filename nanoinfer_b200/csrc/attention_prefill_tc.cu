@@ -407,9 +407,10 @@ extern "C" int nib_attention_prefill_tc(const void* q, int ldq, int T, const voi
                                         const int* entry_start, const int* entry_pos0, int n_head, int n_kv_head,
                                         int head_dim, int page_size, int n_pages, float scale, int window,
                                         int sink, float softcap, int keep_first, const float* slopes, const float* gate,
-                                        int ldg, float out_scale, int* status, cudaStream_t stream) {
+                                        int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (softcap < 0.0f || keep_first < 0) return NIB_ERR_BAD_ARGUMENT;
+  if (span > 0 || head_scale != nullptr || sinks != nullptr) return NIB_ERR_UNSUPPORTED_SIZE;
   const bool plain = !(softcap > 0.0f) && (keep_first <= 0 || window <= 0) && !slopes && !gate && out_scale == 1.0f;
   if (!nib_attention_prefill_tc_supported(head_dim, page_size)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f) || T <= 0) return NIB_ERR_BAD_ARGUMENT;
@@ -426,7 +427,7 @@ extern "C" int nib_attention_prefill_tc(const void* q, int ldq, int T, const voi
   prm.entry_start = entry_start; prm.entry_pos0 = entry_pos0;
   prm.n_head = n_head; prm.n_kv_head = n_kv_head; prm.page_size = page_size; prm.n_pages = n_pages;
   prm.scale = scale; prm.window = window; prm.sink = sink; prm.out = (bf16*)out; prm.ldo = ldo; prm.status = status;
-  prm.ex = AttnExtras{softcap, keep_first, slopes, gate, ldg, out_scale};
+  prm.ex = AttnExtras{softcap, keep_first, slopes, gate, ldg, out_scale, span, head_scale, sinks};
   // 128 keys a tile, one block an SM: measured a little faster than 64 keys a tile and two blocks
   constexpr int BN = 128;
   static bool attr_set = false;

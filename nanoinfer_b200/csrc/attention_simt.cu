@@ -11,7 +11,8 @@
 //
 // Options on the scores and the output (AttnExtras, api.h): a soft cap s <- cap tanh(s / cap); a distance
 // bias s <- s - slope_h (pos - j); with a window, the first `keep_first` keys stay visible behind it (at their
-// true positions); head h's output times sigmoid(gate[t, h]) and times one constant.
+// true positions); head h's output times sigmoid(gate[t, h]) and times one constant; keys of the position's own
+// span only; a scale and a sink's logit per head.
 #include "api.h"
 #include "common.cuh"
 
@@ -42,7 +43,9 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
 
   const int pos = positions[t];
   const int* table = block_table + (size_t)row_entry[t] * max_blocks;
-  const int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  int lo = (window > 0 && pos - window + 1 > 0) ? pos - window + 1 : 0;
+  if (ex.span > 0) lo = max(lo, pos - pos % ex.span);   // only the keys of the position's own span
+  if (ex.head_scale) scale *= ex.head_scale[h];
   const int hk = h / (n_head / n_kv_head);
 
   for (int d = lane; d < head_dim; d += 32) qs[d] = to_float(q[(size_t)t * ldq + h * head_dim + d]);
@@ -102,7 +105,7 @@ attention_simt_kernel(const T* q, int ldq, const T* cache,
   }
   }
   // a sink: one more term in the denominator, a key of score 0 that has no value
-  if (sink) l += expf(-m);
+  if (sink) l += expf((ex.sinks ? ex.sinks[h] : 0.0f) - m);
   float inv = ex.out_scale / l;
   if (ex.gate) inv *= 1.0f / (1.0f + expf(-ex.gate[(size_t)t * ex.ldg + h]));
 #pragma unroll
@@ -121,10 +124,10 @@ extern "C" int nib_attention_simt(int dtype, const void* q, int ldq, const void*
                                   const int* row_entry, const int* positions, int T, int n_head,
                                   int n_kv_head, int head_dim, int page_size, int n_pages,
                                   float scale, int window, int sink, float softcap, int keep_first,
-                                  const float* slopes, const float* gate, int ldg, float out_scale, int* status,
+                                  const float* slopes, const float* gate, int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int* status,
                                   cudaStream_t stream) {
   if (T <= 0) return 0;
-  const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale};
+  const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale, span, head_scale, sinks};
   if (head_dim <= 0 || head_dim > 32 * ATT_MAX_ND || (head_dim & 1)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0) return NIB_ERR_BAD_ARGUMENT;
   if (T > 65535) return NIB_ERR_UNSUPPORTED_SIZE;

@@ -16,7 +16,8 @@ enum : int { DT_F32 = 0, DT_BF16 = 1 };
 
 // activation codes of the linear epilogues
 // (ACT_SILU is taken by the element-wise and expert kernels only, not by the products' epilogues)
-enum : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2, ACT_RELU_SQ = 3, ACT_SILU = 4 };
+// (ACT_SWIGLU_CAPPED is a rule for a gate and a value together: gated_act below)
+enum : int { ACT_NONE = 0, ACT_GELU_TANH = 1, ACT_GELU_ERF = 2, ACT_RELU_SQ = 3, ACT_SILU = 4, ACT_SWIGLU_CAPPED = 5 };
 
 __device__ __forceinline__ float to_float(float v) { return v; }
 __device__ __forceinline__ float to_float(bf16 v) { return __bfloat162float(v); }
@@ -45,6 +46,17 @@ __device__ __forceinline__ float apply_act(float u, int act) {
   if (act == ACT_RELU_SQ) return relu_sq(u);
   if (act == ACT_SILU) return u / (1.0f + expf(-u));
   return u;
+}
+
+// What a gated unit makes of its gate g and its value u: act(g) * u, or, ACT_SWIGLU_CAPPED with the cap `prm`:
+// g' = min(g, prm), u' = clamp(u, -prm, prm), g' sigmoid(1.702 g') (u' + 1).
+__device__ __forceinline__ float gated_act(float g, float u, int act, float prm) {
+  if (act == ACT_SWIGLU_CAPPED) {
+    g = fminf(g, prm);
+    u = fminf(fmaxf(u, -prm), prm);
+    return g / (1.0f + expf(-1.702f * g)) * (u + 1.0f);
+  }
+  return apply_act(g, act) * u;
 }
 
 __device__ __forceinline__ float warp_sum(float v) {

@@ -24,12 +24,13 @@ __device__ __forceinline__ float silu_f32(float v) { return v / (1.0f + expf(-v)
 // out[t, c] = act(bias[c] + sum_j w[c, j] x[t - (taps - 1 - j), c]) for the channels c_off .. c_off + Cn - 1 of proj;
 // inputs before the entry's first row come from the request's state (zeros at the start of a sequence).
 // SHIFT: every entry of the step has one row, and the thread also moves the state on by that row.
+// out16 (may be null): the same values once more as bfloat16, for a matrix product that reads them.
 template <bool SHIFT>
 __global__ void __launch_bounds__(256)
 short_conv_kernel(const float* proj, int ld, int c_off, int Cn, int taps, const float* __restrict__ w,
                   const float* __restrict__ bias, float* state, long long state_stride,
                   const int* __restrict__ row_entry, const int* __restrict__ entry_start,
-                  const int* __restrict__ entry_slot, float* out, int ldo, int act) {
+                  const int* __restrict__ entry_slot, float* out, int ldo, int act, bf16* out16, int ld16) {
   pdl_trigger();
   const int t = blockIdx.y, c = blockIdx.x * blockDim.x + threadIdx.x;
   const int e = row_entry[t];
@@ -43,7 +44,9 @@ short_conv_kernel(const float* proj, int ld, int c_off, int Cn, int taps, const 
     const float xv = src >= 0 ? proj[(size_t)(t - (taps - 1 - j)) * ld + c_off + c] : st[(size_t)(taps - 1 + src) * Cn + c];
     acc = fmaf(w[(size_t)c * taps + j], xv, acc);
   }
-  out[(size_t)t * ldo + c] = act == ACT_SILU ? silu_f32(acc) : acc;
+  const float y = act == ACT_SILU ? silu_f32(acc) : acc;
+  out[(size_t)t * ldo + c] = y;
+  if (out16 != nullptr) out16[(size_t)t * ld16 + c] = __float2bfloat16_rn(y);   // for a product that follows
   if (SHIFT) {
     for (int s = 0; s + 2 < taps; ++s) st[(size_t)s * Cn + c] = st[(size_t)(s + 1) * Cn + c];
     if (taps > 1) st[(size_t)(taps - 2) * Cn + c] = proj[(size_t)t * ld + c_off + c];
@@ -283,17 +286,17 @@ using namespace nib;
 extern "C" int nib_short_conv(const float* proj, int ld, int c_off, int Cn, int taps, const float* w, const float* bias,
                               float* state, long long state_stride, const int* row_entry, const int* entry_start,
                               const int* entry_slot, float* out, int ldo, int T, int n_entries, int act, int fused,
-                              cudaStream_t stream) {
+                              void* out16, int ld16, cudaStream_t stream) {
   if (T <= 0 || Cn <= 0) return 0;
   if (taps < 1 || taps > 64 || T > 65535 || n_entries > 65535) return NIB_ERR_UNSUPPORTED_SIZE;
   const dim3 grid((Cn + 255) / 256, T);
   if (fused) {
     launch_pdl(short_conv_kernel<true>, grid, dim3(256), 0, stream, proj, ld, c_off, Cn, taps, w, bias, state,
-               state_stride, row_entry, entry_start, entry_slot, out, ldo, act);
+               state_stride, row_entry, entry_start, entry_slot, out, ldo, act, (bf16*)out16, ld16);
     NIB_LAUNCH_CHECK();
   }
   launch_pdl(short_conv_kernel<false>, grid, dim3(256), 0, stream, proj, ld, c_off, Cn, taps, w, bias, state,
-             state_stride, row_entry, entry_start, entry_slot, out, ldo, act);
+             state_stride, row_entry, entry_start, entry_slot, out, ldo, act, (bf16*)out16, ld16);
   if (taps > 1 && n_entries > 0)
     launch_pdl(short_conv_state_kernel, dim3((Cn + 255) / 256, n_entries), dim3(256), 0, stream, proj, ld, c_off, Cn,
                taps, state, state_stride, entry_start, entry_slot);

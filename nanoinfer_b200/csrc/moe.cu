@@ -42,13 +42,15 @@ constexpr int MOE_WARPS = 4;
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_route_kernel(const T* h, int ldh, const T* __restrict__ wr, int C, int n_expert, int top, int renorm, int score,
-                 int* ids, float* weights) {
+                 const float* __restrict__ choice_bias, int n_real, float* x, int* ids, float* weights) {
   pdl_trigger();
   extern __shared__ float smem[];
   float* row = smem;               // [C]
   float* prob = smem + C;          // [n_expert]
   __shared__ float scratch[32];
+  __shared__ float pass_on;        // the summed scores of the chosen experts that hand their input on
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  if (threadIdx.x == 0) pass_on = 0.0f;
   pdl_wait();
   for (int c = threadIdx.x; c < C; c += blockDim.x) row[c] = to_float(h[(size_t)t * ldh + c]);
   __syncthreads();
@@ -72,12 +74,12 @@ moe_route_kernel(const T* h, int ldh, const T* __restrict__ wr, int C, int n_exp
     __syncthreads();
   }
   if (warp == 0) {
-    float total = 0.0f;
+    float total = 0.0f, handed = 0.0f;
     for (int k = 0; k < top; ++k) {
       float best = -INFINITY;
       int at = -1;
       for (int e = lane; e < n_expert; e += 32) {
-        const float p = prob[e];
+        const float p = prob[e] + (choice_bias ? choice_bias[e] : 0.0f);   // (the bias moves the choice only)
         if (p > best) { best = p; at = e; }      // (a taken expert holds -inf; a NaN is never larger)
       }
       for (int o = 16; o > 0; o >>= 1) {
@@ -85,18 +87,34 @@ moe_route_kernel(const T* h, int ldh, const T* __restrict__ wr, int C, int n_exp
         const int oa = __shfl_xor_sync(0xffffffffu, at, o);
         if (oa >= 0 && (at < 0 || ob > best || (ob == best && oa < at))) { best = ob; at = oa; }
       }
-      if (at < 0) { at = k % n_expert; best = 0.0f; }   // rows that hold no numbers (rows of no request)
-      else if (score == 1) best = 1.0f / (1.0f + expf(-best));
+      if (at < 0) { at = k % n_real; best = 0.0f; }   // rows that hold no numbers (rows of no request)
+      else {
+        if (choice_bias) best = prob[at];          // the weight is the score itself
+        if (score == 1) best = 1.0f / (1.0f + expf(-best));
+      }
+      // an expert beyond the first n_real has no matrices: it hands its input on, times its score; the expert
+      // kernels skip the id -1
+      if (at >= n_real) handed += best;
+      __syncwarp();
       if (lane == 0) {
-        ids[(size_t)t * top + k] = at;
+        ids[(size_t)t * top + k] = at < n_real ? at : -1;
         weights[(size_t)t * top + k] = best;
         prob[at] = -INFINITY;
       }
       total += best;
       __syncwarp();
     }
-    if (renorm && total > 0.0f)
+    if (renorm && total > 0.0f) {
       for (int k = lane; k < top; k += 32) weights[(size_t)t * top + k] /= total;
+      handed /= total;
+    }
+    if (lane == 0) pass_on = handed;
+  }
+  if (x != nullptr && n_real < n_expert) {
+    __syncthreads();
+    const float wgt = pass_on;
+    if (wgt != 0.0f)
+      for (int c = threadIdx.x; c < C; c += blockDim.x) x[(size_t)t * C + c] += wgt * row[c];
   }
 }
 
@@ -106,12 +124,13 @@ constexpr int MOE_PER_WARP = 2;   // outputs a warp makes one after the other (f
 template <typename T>
 __global__ void __launch_bounds__(MOE_WARPS * 32)
 moe_up_kernel(const T* h, int ldh, const T* __restrict__ w_up, const int* ids, T* inner, int C, int F, int top,
-              int act, int gated, const float* in_weights) {
+              int act, float act_prm, int gated, const float* in_weights) {
   pdl_trigger();
   extern __shared__ float row[];   // [C]
   const int p = blockIdx.x, t = p / top, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_wait();
   const int e = ids[p];
+  if (e < 0) return;               // a choice without matrices: the second product skips it too
   for (int c = threadIdx.x; c < C; c += blockDim.x) row[c] = to_float(h[(size_t)t * ldh + c]);
   __syncthreads();
   const int f0 = (blockIdx.y * MOE_WARPS + warp) * MOE_PER_WARP;
@@ -126,7 +145,7 @@ moe_up_kernel(const T* h, int ldh, const T* __restrict__ w_up, const int* ids, T
       }
       g = warp_sum(g);
       u = warp_sum(u);
-      if (lane == 0) inner[(size_t)p * F + f] = from_float<T>(apply_act(ws * g, act) * (ws * u));
+      if (lane == 0) inner[(size_t)p * F + f] = from_float<T>(gated_act(ws * g, ws * u, act, act_prm));
     }
     return;
   }
@@ -147,13 +166,16 @@ moe_down_kernel(const T* inner, const T* __restrict__ w_down, const int* ids, co
   extern __shared__ float rows[];  // [top][F]
   const int t = blockIdx.x, warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   pdl_wait();
-  for (int i = threadIdx.x; i < top * F; i += blockDim.x) rows[i] = to_float(inner[(size_t)t * top * F + i]);
+  for (int i = threadIdx.x; i < top * F; i += blockDim.x)
+    rows[i] = ids[(size_t)t * top + i / F] < 0 ? 0.0f : to_float(inner[(size_t)t * top * F + i]);
   __syncthreads();
   const int c0 = (blockIdx.y * MOE_WARPS + warp) * MOE_PER_WARP;
   for (int c = c0; c < min(C, c0 + MOE_PER_WARP); ++c) {
     float total = 0.0f;
     for (int k = 0; k < top; ++k) {
-      const T* w = w_down + ((size_t)ids[(size_t)t * top + k] * C + c) * F;
+      const int e = ids[(size_t)t * top + k];
+      if (e < 0) continue;
+      const T* w = w_down + ((size_t)e * C + c) * F;
       const float* r = rows + k * F;
       float s = 0.0f;
       for (int f = lane; f < F; f += 32) s += r[f] * to_float(w[f]);
@@ -174,7 +196,7 @@ constexpr int MOE_G_WARPS = 4, MOE_G_OUT = 32, MOE_G_ROWS = 4;
 template <typename T, typename TO, int MODE>
 __global__ void __launch_bounds__(MOE_G_WARPS * 32)
 moe_grouped_kernel(const T* src, int ld_src, const T* __restrict__ w, const int* ids, const float* weights, TO* out,
-                   int n_pairs, int top, int N, int K, int kp, int act, int chunk) {
+                   int n_pairs, int top, int N, int K, int kp, int act, float act_prm, int chunk) {
   pdl_trigger();
   extern __shared__ __align__(16) unsigned char raw[];
   float4* rows = reinterpret_cast<float4*>(raw);                            // [warps][K]: four inputs side by side
@@ -213,7 +235,7 @@ moe_grouped_kernel(const T* src, int ld_src, const T* __restrict__ w, const int*
         const float other = __shfl_xor_sync(0xffffffffu, v[i], 1);
         if (i < nf && !(lane & 1) && n0 + lane + 1 < N) {
           const float ws = weights ? weights[found[i]] : 1.0f;
-          out[(size_t)found[i] * (N / 2) + (n0 + lane) / 2] = from_float<TO>(apply_act(ws * v[i], act) * (ws * other));
+          out[(size_t)found[i] * (N / 2) + (n0 + lane) / 2] = from_float<TO>(gated_act(ws * v[i], ws * other, act, act_prm));
         }
       }
     } else if (n0 + lane < N) {
@@ -271,7 +293,7 @@ moe_scale_kernel(T* inner, const int* ids, const float* weights, int n_expert, i
 template <typename TI, typename T>
 __global__ void __launch_bounds__(256)
 moe_gate_scale_kernel(const TI* pre, T* inner, const int* ids, const float* weights, int n_expert, int F, int top,
-                      int act, int on_input, size_t n) {
+                      int act, float act_prm, int on_input, size_t n) {
   pdl_trigger();
   pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
@@ -285,19 +307,21 @@ moe_gate_scale_kernel(const TI* pre, T* inner, const int* ids, const float* weig
   float v = 0.0f;
   if (chosen) {
     const float g = to_float(pre[2 * i]), u = to_float(pre[2 * i + 1]);
-    v = on_input ? apply_act(s * g, act) * (s * u) : s * apply_act(g, act) * u;
+    v = on_input ? gated_act(s * g, s * u, act, act_prm) : s * gated_act(g, u, act, act_prm);
   }
   inner[i] = from_float<T>(v);
 }
 
-__global__ void __launch_bounds__(256) moe_combine_kernel(const float* parts, float* x, int C, int top, size_t n) {
+__global__ void __launch_bounds__(256) moe_combine_kernel(const float* parts, const int* ids, float* x, int C, int top,
+                                                          size_t n) {
   pdl_trigger();
   pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= n) return;
   const size_t t = i / C, c = i % C;
   float total = 0.0f;
-  for (int k = 0; k < top; ++k) total += parts[(t * top + k) * C + c];
+  for (int k = 0; k < top; ++k)
+    if (ids == nullptr || ids[t * top + k] >= 0) total += parts[(t * top + k) * C + c];
   x[i] += total;
 }
 
@@ -313,7 +337,7 @@ template <typename T> static size_t moe_grouped_smem(int K) {
 
 template <typename T, typename TO, int MODE>
 static int launch_moe_grouped(const T* src, int ld_src, const T* w, const int* ids, const float* weights, TO* out,
-                              int n_pairs, int top, int n_expert, int N, int K, int act, cudaStream_t stream) {
+                              int n_pairs, int top, int n_expert, int N, int K, int act, float act_prm, cudaStream_t stream) {
   const size_t smem = moe_grouped_smem<T>(K);
   if (smem > 200 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
   if (smem > 48 * 1024)
@@ -323,7 +347,7 @@ static int launch_moe_grouped(const T* src, int ld_src, const T* w, const int* i
   const int chunk = ((n_pairs + z - 1) / z + 31) / 32 * 32;
   launch_pdl(moe_grouped_kernel<T, TO, MODE>, dim3(n_expert, (N + MOE_G_OUT - 1) / MOE_G_OUT, (n_pairs + chunk - 1) / chunk),
              dim3(MOE_G_WARPS * 32), smem, stream, src, ld_src, w, ids, weights, out, n_pairs, top, N, K,
-             moe_padded<T>(K), act, chunk);
+             moe_padded<T>(K), act, act_prm, chunk);
   NIB_LAUNCH_CHECK();
 }
 
@@ -336,50 +360,52 @@ using namespace nib;
 // a row's parts into the stream (phase 2).  -2 where a tile of an expert's matrix does not fit shared memory.
 extern "C" int nib_moe_grouped(int dtype, int phase, const void* src, int ld_src, const void* w, const int* ids,
                                const float* weights, void* out, float* x, int T, int top, int n_expert, int N, int K,
-                               int act, cudaStream_t stream) {
+                               int act, float act_prm, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (phase == 2) {
     const size_t n = (size_t)T * N;
-    launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)src, x, N, top, n);
+    launch_pdl(moe_combine_kernel, dim3((unsigned)((n + 255) / 256)), dim3(256), 0, stream, (const float*)src, ids, x, N, top, n);
     NIB_LAUNCH_CHECK();
   }
   if (dtype == DT_F32) {
     if (phase == 3)
       return launch_moe_grouped<float, float, 2>((const float*)src, ld_src, (const float*)w, ids, weights, (float*)out,
-                                                 T * top, top, n_expert, N, K, act, stream);
+                                                 T * top, top, n_expert, N, K, act, act_prm, stream);
     if (phase == 0)
       return launch_moe_grouped<float, float, 0>((const float*)src, ld_src, (const float*)w, ids, weights, (float*)out,
-                                                 T * top, top, n_expert, N, K, act, stream);
+                                                 T * top, top, n_expert, N, K, act, act_prm, stream);
     return launch_moe_grouped<float, float, 1>((const float*)src, ld_src, (const float*)w, ids, weights, (float*)out,
-                                               T * top, top, n_expert, N, K, act, stream);
+                                               T * top, top, n_expert, N, K, act, act_prm, stream);
   }
   if (dtype == DT_BF16) {
     if (phase == 3)
       return launch_moe_grouped<bf16, bf16, 2>((const bf16*)src, ld_src, (const bf16*)w, ids, weights, (bf16*)out,
-                                               T * top, top, n_expert, N, K, act, stream);
+                                               T * top, top, n_expert, N, K, act, act_prm, stream);
     if (phase == 0)
       return launch_moe_grouped<bf16, bf16, 0>((const bf16*)src, ld_src, (const bf16*)w, ids, weights, (bf16*)out,
-                                               T * top, top, n_expert, N, K, act, stream);
+                                               T * top, top, n_expert, N, K, act, act_prm, stream);
     return launch_moe_grouped<bf16, float, 1>((const bf16*)src, ld_src, (const bf16*)w, ids, weights, (float*)out,
-                                              T * top, top, n_expert, N, K, act, stream);
+                                              T * top, top, n_expert, N, K, act, act_prm, stream);
   }
   return NIB_ERR_BAD_ARGUMENT;
 }
 
 extern "C" int nib_moe_route(int dtype, const void* h, int ldh, const void* w_router, int T, int C, int n_expert,
-                             int top, int renorm, int score, int* ids, float* weights, cudaStream_t stream) {
+                             int top, int renorm, int score, const float* choice_bias, int n_real, float* x, int* ids,
+                             float* weights, cudaStream_t stream) {
   if (T <= 0) return 0;
   if (top <= 0 || top > n_expert || C <= 0 || (score != 0 && score != 1)) return NIB_ERR_BAD_ARGUMENT;
+  if (n_real <= 0 || n_real > n_expert || (n_real < n_expert && x == nullptr)) return NIB_ERR_BAD_ARGUMENT;
   const size_t smem = (size_t)(C + n_expert) * sizeof(float);
   if (smem > 200 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
   if (dtype == DT_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(moe_route_kernel<float>, dim3(T), dim3(MOE_WARPS * 32), smem, stream, (const float*)h, ldh,
-               (const float*)w_router, C, n_expert, top, renorm, score, ids, weights);
+               (const float*)w_router, C, n_expert, top, renorm, score, choice_bias, n_real, x, ids, weights);
   } else if (dtype == DT_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_route_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(moe_route_kernel<bf16>, dim3(T), dim3(MOE_WARPS * 32), smem, stream, (const bf16*)h, ldh,
-               (const bf16*)w_router, C, n_expert, top, renorm, score, ids, weights);
+               (const bf16*)w_router, C, n_expert, top, renorm, score, choice_bias, n_real, x, ids, weights);
   } else {
     return NIB_ERR_BAD_ARGUMENT;
   }
@@ -389,7 +415,7 @@ extern "C" int nib_moe_route(int dtype, const void* h, int ldh, const void* w_ro
 // inner: [T * top, F] in `dtype`; act: an activation code.  gated: w_up is [experts, 2F, C] with rows 2f, 2f + 1 the
 // gate and value of output f, and in_weights (may be null) [T * top] scale the inputs.
 extern "C" int nib_moe_up(int dtype, const void* h, int ldh, const void* w_up, const int* ids, void* inner, int T,
-                          int C, int F, int top, int act, int gated, const float* in_weights, cudaStream_t stream) {
+                          int C, int F, int top, int act, float act_prm, int gated, const float* in_weights, cudaStream_t stream) {
   if (T <= 0) return 0;
   const size_t smem = (size_t)C * sizeof(float);
   if (smem > 200 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
@@ -398,11 +424,11 @@ extern "C" int nib_moe_up(int dtype, const void* h, int ldh, const void* w_up, c
   if (dtype == DT_F32) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_kernel<float>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(moe_up_kernel<float>, grid, dim3(MOE_WARPS * 32), smem, stream, (const float*)h, ldh,
-               (const float*)w_up, ids, (float*)inner, C, F, top, act, gated, in_weights);
+               (const float*)w_up, ids, (float*)inner, C, F, top, act, act_prm, gated, in_weights);
   } else if (dtype == DT_BF16) {
     if (smem > 48 * 1024) cudaFuncSetAttribute(moe_up_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     launch_pdl(moe_up_kernel<bf16>, grid, dim3(MOE_WARPS * 32), smem, stream, (const bf16*)h, ldh, (const bf16*)w_up,
-               ids, (bf16*)inner, C, F, top, act, gated, in_weights);
+               ids, (bf16*)inner, C, F, top, act, act_prm, gated, in_weights);
   } else {
     return NIB_ERR_BAD_ARGUMENT;
   }
@@ -433,20 +459,20 @@ extern "C" int nib_moe_down(int dtype, const void* inner, const void* w_down, co
 
 // pre: [T, n_expert * 2F] in `pre_dtype` (32-bit floats or `dtype`); inner [T, n_expert * F] in `dtype`.
 extern "C" int nib_moe_gate_scale(int pre_dtype, int dtype, const void* pre, void* inner, const int* ids,
-                                  const float* weights, int T, int n_expert, int F, int top, int act, int on_input,
-                                  cudaStream_t stream) {
+                                  const float* weights, int T, int n_expert, int F, int top, int act, float act_prm,
+                                  int on_input, cudaStream_t stream) {
   if (T <= 0) return 0;
   const size_t n = (size_t)T * n_expert * F;
   const dim3 grid((unsigned)((n + 255) / 256));
   if (pre_dtype == DT_F32 && dtype == DT_F32)
     launch_pdl(moe_gate_scale_kernel<float, float>, grid, dim3(256), 0, stream, (const float*)pre, (float*)inner, ids,
-               weights, n_expert, F, top, act, on_input, n);
+               weights, n_expert, F, top, act, act_prm, on_input, n);
   else if (pre_dtype == DT_F32 && dtype == DT_BF16)
     launch_pdl(moe_gate_scale_kernel<float, bf16>, grid, dim3(256), 0, stream, (const float*)pre, (bf16*)inner, ids,
-               weights, n_expert, F, top, act, on_input, n);
+               weights, n_expert, F, top, act, act_prm, on_input, n);
   else if (pre_dtype == DT_BF16 && dtype == DT_BF16)
     launch_pdl(moe_gate_scale_kernel<bf16, bf16>, grid, dim3(256), 0, stream, (const bf16*)pre, (bf16*)inner, ids,
-               weights, n_expert, F, top, act, on_input, n);
+               weights, n_expert, F, top, act, act_prm, on_input, n);
   else
     return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();

@@ -212,3 +212,168 @@ extern "C" int nib_norm_rope_append(int dtype, const float* proj, int ld, int q_
     return NIB_ERR_BAD_ARGUMENT;
   NIB_LAUNCH_CHECK();
 }
+
+// ---------------------------------------------------------------------------------------------------------------
+// The halves layout: of a head's first `rot_dims` values, value i is paired with value i + rot_dims / 2 and the
+// pair (u, w) at position p becomes (u cos a - w sin a, w cos a + u sin a), a = p * freqs[i]; the other values pass.
+namespace nib {
+
+// Queries and keys normed over the WHOLE projection (all heads at once: x / sqrt(mean(x^2) + eps) times a weight of
+// the projection's size; null: no norm), then turned in the halves layout, cast, padded to the cache's head size and
+// written: queries to q_out, keys to plane 0 of the row's cache slot; plane 1 receives the values, which are read as
+// they stand (v_off may name the keys' own columns: a layer whose values are its keys ahead of norm and rotation).
+// A block a row.
+template <typename T>
+__global__ void __launch_bounds__(256)
+wide_norm_rope_append_kernel(const float* src, int ld, int q_off, int k_off, int v_off, int n_head, int n_kv_head,
+                             int dim, int vdim, int hd, const float* __restrict__ wq, const float* __restrict__ wk,
+                             float eps, int rot_dims, const double* __restrict__ freqs,
+                             const int* __restrict__ positions, const int* __restrict__ row_entry, T* q_out, int ldq,
+                             T* cache, const int* __restrict__ block_table, int max_blocks, int page_size, int n_pages,
+                             int* status) {
+  pdl_trigger();
+  extern __shared__ float cs[];          // [rot_dims / 2] cosines, then as many sines
+  __shared__ float scratch[32];
+  const int t = blockIdx.x, half = rot_dims / 2;
+  const int pos = positions[t], entry = row_entry[t];
+  float* sn = cs + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double sd, cd;
+    sincos((double)pos * freqs[i], &sd, &cd);
+    cs[i] = (float)cd;
+    sn[i] = (float)sd;
+  }
+  T* k_dst = nullptr;
+  T* v_dst = nullptr;
+  if (entry >= 0 && cache != nullptr) {
+    const int page = block_table[(size_t)entry * max_blocks + pos / page_size];
+    if (page < 0 || page >= n_pages) {
+      if (threadIdx.x == 0) *status = NIB_STATUS_BAD_PAGE;
+    } else {
+      k_dst = cache + kv_offset(page, 0, 0, pos % page_size, n_kv_head, page_size, hd);
+      v_dst = cache + kv_offset(page, 1, 0, pos % page_size, n_kv_head, page_size, hd);
+    }
+  }
+  const size_t head_stride = (size_t)page_size * hd;
+  pdl_wait();
+  const float* p = src + (size_t)t * ld;
+  const int nq = n_head * dim, nk = n_kv_head * dim;
+  float sq = 0.0f, sk = 0.0f;
+  if (wq != nullptr)
+    for (int i = threadIdx.x; i < nq; i += blockDim.x) sq += p[q_off + i] * p[q_off + i];
+  if (wk != nullptr && k_dst != nullptr)
+    for (int i = threadIdx.x; i < nk; i += blockDim.x) sk += p[k_off + i] * p[k_off + i];
+  const float rq = wq != nullptr ? 1.0f / sqrtf(block_sum(sq, scratch) / (float)nq + eps) : 1.0f;
+  const float rk = wk != nullptr ? 1.0f / sqrtf(block_sum(sk, scratch) / (float)nk + eps) : 1.0f;
+  __syncthreads();
+  const int n_rot = (n_head + (k_dst != nullptr ? n_kv_head : 0)) * hd;
+  for (int idx = threadIdx.x; idx < n_rot; idx += blockDim.x) {
+    const int hh = idx / hd, c = idx % hd;
+    const bool is_q = hh < n_head;
+    const int h = is_q ? hh : hh - n_head;
+    const float* x = p + (is_q ? q_off : k_off) + h * dim;
+    const float* w = is_q ? wq : wk;
+    const float r = is_q ? rq : rk;
+    float v = 0.0f;
+    if (c < dim) {
+      v = x[c] * r;
+      if (w != nullptr) v *= w[h * dim + c];
+      if (c < rot_dims) {
+        const int pc = c < half ? c + half : c - half, i = c < half ? c : c - half;
+        float o = x[pc] * r;
+        if (w != nullptr) o *= w[h * dim + pc];
+        v = c < half ? v * cs[i] - o * sn[i] : v * cs[i] + o * sn[i];
+      }
+    }
+    if (is_q) q_out[(size_t)t * ldq + (size_t)h * hd + c] = from_float<T>(v);
+    else k_dst[h * head_stride + c] = from_float<T>(v);
+  }
+  if (v_dst != nullptr)
+    for (int idx = threadIdx.x; idx < n_kv_head * hd; idx += blockDim.x) {
+      const int h = idx / hd, c = idx % hd;
+      v_dst[h * head_stride + c] = from_float<T>(c < vdim ? p[v_off + h * vdim + c] : 0.0f);
+    }
+}
+
+// In place on 32-bit rows: the query and key heads (n_head of `dim` values each at q_off and at k_off) turned in the
+// halves layout, the keys then times k_mul; and coef[t, h] = (decay[h], 1): what a recurrence with one fixed decay
+// per head reads as its rows' decays and strengths.  A block a row; a thread owns a pair (or a value that passes).
+__global__ void __launch_bounds__(256)
+rope_halves_kernel(float* rows, int ld, int q_off, int k_off, int n_head, int dim, int rot_dims,
+                   const double* __restrict__ freqs, const int* __restrict__ positions, float k_mul,
+                   const float* __restrict__ decay, float* coef) {
+  pdl_trigger();
+  extern __shared__ float cs[];
+  const int t = blockIdx.x, half = rot_dims / 2;
+  const int pos = positions[t];
+  float* sn = cs + half;
+  for (int i = threadIdx.x; i < half; i += blockDim.x) {
+    double sd, cd;
+    sincos((double)pos * freqs[i], &sd, &cd);
+    cs[i] = (float)cd;
+    sn[i] = (float)sd;
+  }
+  if (coef != nullptr)
+    for (int h = threadIdx.x; h < n_head; h += blockDim.x) {
+      coef[((size_t)t * n_head + h) * 2] = decay[h];
+      coef[((size_t)t * n_head + h) * 2 + 1] = 1.0f;
+    }
+  __syncthreads();
+  pdl_wait();
+  float* p = rows + (size_t)t * ld;
+  const int units = dim - half;            // per head: `half` pairs, then the values behind rot_dims
+  for (int idx = threadIdx.x; idx < 2 * n_head * units; idx += blockDim.x) {
+    const int hh = idx / units, u = idx % units;
+    const bool is_q = hh < n_head;
+    float* x = p + (is_q ? q_off : k_off) + (is_q ? hh : hh - n_head) * dim;
+    const float mul = is_q ? 1.0f : k_mul;
+    if (u < half) {
+      const float a = x[u], b = x[u + half];
+      x[u] = (a * cs[u] - b * sn[u]) * mul;
+      x[u + half] = (b * cs[u] + a * sn[u]) * mul;
+    } else {
+      x[u + half] *= mul;
+    }
+  }
+}
+
+}  // namespace nib
+
+extern "C" int nib_wide_norm_rope_append(int dtype, const float* src, int ld, int q_off, int k_off, int v_off,
+                                         int n_head, int n_kv_head, int dim, int vdim, int hd, const float* wq,
+                                         const float* wk, float eps, int rot_dims, const double* freqs,
+                                         const int* positions, const int* row_entry, void* q_out, int ldq, void* cache,
+                                         const int* block_table, int max_blocks, int page_size, int n_pages, int T,
+                                         int* status, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dim <= 0 || vdim <= 0 || dim > hd || vdim > hd || rot_dims < 0 || rot_dims > dim || (rot_dims & 1))
+    return NIB_ERR_BAD_ARGUMENT;
+  if (rot_dims > 0 && freqs == nullptr) return NIB_ERR_BAD_ARGUMENT;
+  const size_t smem = (size_t)rot_dims * sizeof(float);
+  if (smem > 48 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
+  if (dtype == DT_F32)
+    launch_pdl(wide_norm_rope_append_kernel<float>, dim3(T), dim3(256), smem, stream, src, ld, q_off, k_off, v_off,
+               n_head, n_kv_head, dim, vdim, hd, wq, wk, eps, rot_dims, freqs, positions, row_entry, (float*)q_out, ldq,
+               (float*)cache, block_table, max_blocks, page_size, n_pages, status);
+  else if (dtype == DT_BF16)
+    launch_pdl(wide_norm_rope_append_kernel<bf16>, dim3(T), dim3(256), smem, stream, src, ld, q_off, k_off, v_off,
+               n_head, n_kv_head, dim, vdim, hd, wq, wk, eps, rot_dims, freqs, positions, row_entry, (bf16*)q_out, ldq,
+               (bf16*)cache, block_table, max_blocks, page_size, n_pages, status);
+  else
+    return NIB_ERR_BAD_ARGUMENT;
+  NIB_LAUNCH_CHECK();
+}
+
+extern "C" int nib_rope_halves(float* rows, int ld, int q_off, int k_off, int n_head, int dim, int rot_dims,
+                               const double* freqs, const int* positions, float k_mul, const float* decay, float* coef,
+                               int T, cudaStream_t stream) {
+  if (T <= 0) return 0;
+  if (dim <= 0 || rot_dims < 0 || rot_dims > dim || (rot_dims & 1) || (rot_dims > 0 && freqs == nullptr) ||
+      (coef != nullptr && decay == nullptr))
+    return NIB_ERR_BAD_ARGUMENT;
+  const size_t smem = (size_t)rot_dims * sizeof(float);
+  if (smem > 48 * 1024) return NIB_ERR_UNSUPPORTED_SIZE;
+  launch_pdl(rope_halves_kernel, dim3(T), dim3(256), smem, stream, rows, ld, q_off, k_off, n_head, dim, rot_dims, freqs,
+             positions, k_mul, decay, coef);
+  NIB_LAUNCH_CHECK();
+}

@@ -208,7 +208,7 @@ glu_kernel(const InT* pre, int ld, OutT* out, int ldo, int n_rows, int F, int ac
   out[(size_t)t * ldo + f] = from_float<OutT>(v);
 }
 
-enum : int { UNARY_TANH = 1, UNARY_XIELU = 2, UNARY_SOFTCAP = 3 };   // softcap: prm[0] tanh(z / prm[0])
+enum : int { UNARY_TANH = 1, UNARY_XIELU = 2, UNARY_SOFTCAP = 3, UNARY_SCALE = 4 };   // softcap: prm[0] tanh(z / prm[0]); scale: prm[0] z
 
 __device__ __forceinline__ float softplus_f(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
 
@@ -222,7 +222,7 @@ unary_kernel(const InT* in, int ld_in, OutT* out, int ld_out, int n_rows, int n_
     sp = softplus_f(prm[0]);
     sq = 0.5f + softplus_f(prm[1]);
   }
-  if (kind == UNARY_SOFTCAP) sp = prm[0];
+  if (kind == UNARY_SOFTCAP || kind == UNARY_SCALE) sp = prm[0];
   pdl_wait();
   const size_t i = (size_t)blockIdx.x * blockDim.x + threadIdx.x;
   if (i >= (size_t)n_rows * n_cols) return;
@@ -233,6 +233,8 @@ unary_kernel(const InT* in, int ld_in, OutT* out, int ld_out, int n_rows, int n_
     y = tanhf(z);
   else if (kind == UNARY_SOFTCAP)
     y = sp * tanhf(z / sp);
+  else if (kind == UNARY_SCALE)
+    y = sp * z;
   else
     y = z > 0.0f ? sp * z * z + 0.5f * z : sq * (expm1f(z) - z) + 0.5f * z;
   out[(size_t)r * ld_out + c] = from_float<OutT>(y);
@@ -350,7 +352,7 @@ extern "C" int nib_glu(int in_dtype, int out_dtype, const void* pre, int ld, voi
 extern "C" int nib_unary(int in_dtype, int out_dtype, const void* in, int ld_in, void* out, int ld_out, int n_rows,
                          int n_cols, int kind, const float* prm, cudaStream_t stream) {
   if (n_rows <= 0 || n_cols <= 0) return 0;
-  if (kind != UNARY_TANH && kind != UNARY_XIELU && kind != UNARY_SOFTCAP) return NIB_ERR_BAD_ARGUMENT;
+  if (kind != UNARY_TANH && kind != UNARY_XIELU && kind != UNARY_SOFTCAP && kind != UNARY_SCALE) return NIB_ERR_BAD_ARGUMENT;
   if (kind != UNARY_TANH && prm == nullptr) return NIB_ERR_BAD_ARGUMENT;
   const size_t n = (size_t)n_rows * n_cols;
   const dim3 grid((unsigned)((n + 255) / 256));

@@ -14,11 +14,12 @@ import torch
 
 from . import build as _build
 
-ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU_SQ, ACT_SILU = 0, 1, 2, 3, 4
-#: (the products' epilogues take all but "silu", which the element-wise and expert kernels apply)
+ACT_NONE, ACT_GELU_TANH, ACT_GELU_ERF, ACT_RELU_SQ, ACT_SILU, ACT_SWIGLU_CAPPED = 0, 1, 2, 3, 4, 5
+#: (the products' epilogues take all but "silu", which the element-wise and expert kernels apply, and
+#: "swiglu_capped", a rule for a gated unit's gate and value together that the expert kernels apply)
 ACT_CODES = {None: ACT_NONE, "none": ACT_NONE, "tanh": ACT_GELU_TANH, "erf": ACT_GELU_ERF, "relu2": ACT_RELU_SQ,
-             "silu": ACT_SILU}
-UNARY_TANH, UNARY_XIELU, UNARY_SOFTCAP = 1, 2, 3
+             "silu": ACT_SILU, "swiglu_capped": ACT_SWIGLU_CAPPED}
+UNARY_TANH, UNARY_XIELU, UNARY_SOFTCAP, UNARY_SCALE = 1, 2, 3, 4
 
 STATUS_OK, STATUS_BAD_PAGE, STATUS_WAIT_TIMEOUT = 0, 1, 2
 _ERR_NAMES = {-1: "bad argument", -2: "unsupported size", -3: "CUDA driver call failed"}
@@ -57,13 +58,14 @@ _SIGNATURES = {
     "nib_attention_prefill_tc_supported": [_c_int, _c_int],
     "nib_attention_prefill_tc": [_c_ptr, _c_int, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr,
                                  _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_float, _c_int,
-                                 _c_ptr, _c_ptr, _c_int, _c_float, _c_ptr, _c_ptr],
+                                 _c_ptr, _c_ptr, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "nib_attention_simt": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
                            _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_float, _c_int,
-                           _c_ptr, _c_ptr, _c_int, _c_float, _c_ptr, _c_ptr],
+                           _c_ptr, _c_ptr, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "nib_attention_decode": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                              _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_float,
-                             _c_int, _c_ptr, _c_ptr, _c_int, _c_float, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr],
+                             _c_int, _c_ptr, _c_ptr, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr, _c_ptr,
+                             _c_ptr],
     "nib_attention_decode_mma_supported": [_c_int, _c_int],
     "nib_attention_decode_mma_clusters": [_c_int, _c_int],
     "nib_attention_decode_mma": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr,
@@ -72,7 +74,7 @@ _SIGNATURES = {
     "nib_attention_prefill_supported": [_c_int],
     "nib_attention_prefill": [_c_ptr, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr,
                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_float, _c_int, _c_int, _c_float, _c_int,
-                              _c_ptr, _c_ptr, _c_int, _c_float, _c_ptr, _c_ptr],
+                              _c_ptr, _c_ptr, _c_int, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr],
     "nib_convert": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_ptr],
     "nib_argmax": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_sample": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int,
@@ -94,12 +96,12 @@ _SIGNATURES = {
     "nib_delta_rule": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
                        _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_float, _c_ptr, _c_int,
                        _c_ptr, _c_ptr],
-    "nib_moe_route": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr,
-                      _c_ptr],
-    "nib_moe_up": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
-                   _c_ptr, _c_ptr],
+    "nib_moe_route": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int,
+                      _c_ptr, _c_ptr, _c_ptr, _c_ptr],
+    "nib_moe_up": [_c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_float,
+                   _c_int, _c_ptr, _c_ptr],
     "nib_moe_gate_scale": [_c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
-                           _c_int, _c_ptr],
+                           _c_float, _c_int, _c_ptr],
     "nib_add_norm": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int, _c_ptr],
     "nib_glu": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_rope_append": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
@@ -115,7 +117,7 @@ _SIGNATURES = {
                              _c_ptr, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_int,
                              _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
     "nib_short_conv": [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, ctypes.c_longlong, _c_ptr, _c_ptr,
-                       _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr],
+                       _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr],
     "nib_scan_prepare": [_c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int,
                          _c_int, _c_int, _c_ptr, _c_int, _c_ptr],
     "nib_gated_scan_padded": [_c_int],
@@ -126,7 +128,19 @@ _SIGNATURES = {
     "nib_moe_down": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_scale": [_c_int, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_ptr],
     "nib_moe_grouped": [_c_int, _c_int, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
-                        _c_int, _c_int, _c_int, _c_ptr],
+                        _c_int, _c_int, _c_int, _c_float, _c_ptr],
+    "nib_wide_norm_rope_append": [_c_int, _c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                  _c_ptr, _c_ptr, _c_float, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr,
+                                  _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr],
+    "nib_rope_halves": [_c_ptr, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_ptr,
+                        _c_int, _c_ptr],
+    "nib_hyper_enter": [_c_int, _c_ptr, _c_ptr, ctypes.c_longlong, _c_int, _c_ptr, _c_ptr, _c_float, _c_ptr, _c_int, _c_int,
+                        _c_ptr],
+    "nib_hyper_update": [_c_int, _c_ptr, ctypes.c_longlong, _c_int, _c_ptr, _c_ptr, _c_int, _c_ptr, _c_ptr, _c_ptr, _c_ptr,
+                         _c_float, _c_ptr, _c_ptr, _c_int, _c_int, _c_ptr],
+    "nib_selective_scan": [_c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_ptr, _c_int, _c_int, _c_int, _c_ptr, _c_int, _c_ptr,
+                           _c_ptr, _c_ptr, ctypes.c_longlong, ctypes.c_longlong, _c_ptr, _c_ptr, _c_int, _c_int, _c_int,
+                           _c_ptr, _c_int, _c_ptr],
 }
 
 
@@ -632,28 +646,36 @@ class AttnExtras:
     ``softcap`` > 0: s <- softcap tanh(s / softcap) after the scale; ``slopes`` (float32 [n_head]): s <- s -
     slopes[h] (query position - key position); ``keep_first``: with a window, the keys 0 .. keep_first - 1 stay
     visible behind it; ``gate`` (float32 [rows, >= n_head], any row stride): head h's output of row t times
-    sigmoid(gate[t, h]); ``out_scale``: and times this constant."""
+    sigmoid(gate[t, h]); ``out_scale``: and times this constant; ``span`` > 0: position i sees key j only if
+    i // span == j // span (spans count from position 0 of the sequence); ``head_scale`` (float32 [n_head]): the
+    scale times head_scale[h]; ``sinks`` (float32 [n_head]): with a sink, its term of the denominator is
+    exp(sinks[h]) instead of exp(0)."""
 
-    __slots__ = ("softcap", "keep_first", "slopes", "gate", "out_scale")
+    __slots__ = ("softcap", "keep_first", "slopes", "gate", "out_scale", "span", "head_scale", "sinks")
 
     def __init__(self, softcap: float = 0.0, keep_first: int = 0, slopes: Optional[torch.Tensor] = None,
-                 gate: Optional[torch.Tensor] = None, out_scale: float = 1.0):
+                 gate: Optional[torch.Tensor] = None, out_scale: float = 1.0, span: int = 0,
+                 head_scale: Optional[torch.Tensor] = None, sinks: Optional[torch.Tensor] = None):
         self.softcap, self.keep_first, self.slopes = float(softcap), int(keep_first), slopes
         self.gate, self.out_scale = gate, float(out_scale)
+        self.span, self.head_scale, self.sinks = int(span), head_scale, sinks
 
     @property
     def plain(self) -> bool:
         return not (self.softcap > 0.0 or self.keep_first > 0 or self.slopes is not None or self.gate is not None
-                    or self.out_scale != 1.0)
+                    or self.out_scale != 1.0 or self.span > 0 or self.head_scale is not None or self.sinks is not None)
 
     def args(self) -> tuple:
         g = self.gate
         if g is not None and (g.dtype != torch.float32 or g.stride(1) != 1):
             raise KernelError("attention: the output gate must be float32 with contiguous rows")
-        if self.slopes is not None and self.slopes.dtype != torch.float32:
-            raise KernelError("attention: the slopes must be float32")
+        for t in (self.slopes, self.head_scale, self.sinks):
+            if t is not None and (t.dtype != torch.float32 or not t.is_contiguous()):
+                raise KernelError("attention: the slopes, the heads' scales and the sinks must be contiguous float32")
+        if self.span < 0:
+            raise KernelError("attention: span must not be negative")
         return (self.softcap, self.keep_first, _ptr(self.slopes), _ptr(g), g.stride(0) if g is not None else 0,
-                self.out_scale)
+                self.out_scale, self.span, _ptr(self.head_scale), _ptr(self.sinks))
 
 
 _NO_EXTRAS = AttnExtras()
@@ -876,6 +898,8 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
         return
     if plan.n_decode:
         keys = plan.max_decode_keys if window <= 0 else min(plan.max_decode_keys, window)
+        if extras is not None and extras.span > 0:
+            keys = min(keys, extras.span)
         if traced:
             _note_attention(plan.n_decode, plan.decode_keys, plan.decode_keys, n_head, n_kv_head, head_dim,
                             q.element_size())
@@ -885,12 +909,13 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
         if traced:
             _note_attention(plan.n_prefill_rows, plan.prefill_keys, plan.prefill_kv_rows, n_head, n_kv_head, head_dim,
                             q.element_size())
-        if q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
+        tiled = extras is None or (extras.span <= 0 and extras.head_scale is None and extras.sinks is None)
+        if tiled and q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 \
                 and out.data_ptr() % 16 == 0:
             attention_prefill_tc(q, cache, out, block_table, plan.wide_tiles, plan.n_wide_tiles, ctx.entry_start,
                                  ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status, sink=sink, extras=extras)
-        elif q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
+        elif tiled and q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
             attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
                               n_head, scale, window, ctx.status, sink=sink, extras=extras)
@@ -1156,24 +1181,34 @@ def delta_rule(proj: torch.Tensor, offsets, wl: torch.Tensor, w0: torch.Tensor, 
 
 # ------------------------------------------------------------------------------ routed experts
 def moe_route(h: torch.Tensor, w_router: torch.Tensor, T: int, top: int, renorm: bool, ids: torch.Tensor,
-              weights: torch.Tensor, score: str = "softmax") -> None:
+              weights: torch.Tensor, score: str = "softmax", choice_bias: Optional[torch.Tensor] = None,
+              n_real: Optional[int] = None, x: Optional[torch.Tensor] = None) -> None:
     """Router logits in 32-bit, scores = softmax over all experts (or, ``score`` "sigmoid", each logit's sigmoid),
     the ``top`` largest (ties to the lower index) into ``ids`` int32 [T, top] with their scores in ``weights``
-    float32 [T, top] (divided by their sum with ``renorm``)."""
+    float32 [T, top] (divided by their sum with ``renorm``).  ``choice_bias`` (float32 [experts]) is added to the
+    scores for the choice only.  The experts from ``n_real`` on have no matrices: a row that chooses one gets
+    score * h[t] added to ``x`` (float32 [T, C]) right here, and the id -1, which the expert kernels skip."""
     if score not in ("softmax", "sigmoid"):
         raise KernelError("moe_route: score is 'softmax' or 'sigmoid'")
     E, C = w_router.shape
     if h.dtype != w_router.dtype or h.stride(1) != 1 or not w_router.is_contiguous():
         raise KernelError("moe_route: h and the router share a dtype")
     _i32(ids, "ids"); _f32(weights, "moe_route: weights")
+    n_real = E if n_real is None else int(n_real)
+    if choice_bias is not None and (choice_bias.dtype != torch.float32 or choice_bias.numel() != E
+                                    or not choice_bias.is_contiguous()):
+        raise KernelError("moe_route: choice_bias must be contiguous float32 [experts]")
+    if n_real < E and (x is None or x.dtype != torch.float32 or not x.is_contiguous() or x.shape[1] != C):
+        raise KernelError("moe_route: experts without matrices need the 32-bit x [T, C] to add into")
     if tracing():
         _note("matmul", "router", (T, C, E), 2.0 * T * C * E, (E + T) * C * h.element_size() + 8.0 * T * top)
     _check(library().nib_moe_route(_dt(h), _ptr(h), h.stride(0), _ptr(w_router), T, C, E, top, int(renorm),
-                                   int(score == "sigmoid"), _ptr(ids), _ptr(weights), _stream()), "moe_route")
+                                   int(score == "sigmoid"), _ptr(choice_bias), n_real, _ptr(x) if n_real < E else None, _ptr(ids),
+                                   _ptr(weights), _stream()), "moe_route")
 
 
 def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, inner: torch.Tensor, T: int, top: int,
-           act: int, gated: bool = False, in_weights: Optional[torch.Tensor] = None) -> None:
+           act: int, gated: bool = False, in_weights: Optional[torch.Tensor] = None, act_prm: float = 0.0) -> None:
     """inner[t * top + k] = act(w_up[ids[t, k]] . h[t]) for w_up [experts, F, C].  ``gated``: w_up is
     [experts, 2F, C] with rows 2f and 2f + 1 the gate and the value of output f, and inner = act(s g) * (s u) with
     s = in_weights[t, k] (None: 1)."""
@@ -1187,7 +1222,7 @@ def moe_up(h: torch.Tensor, w_up: torch.Tensor, ids: torch.Tensor, inner: torch.
         _note("moe", "experts_up", (T * top, C, F), 2.0 * T * top * C * F,
               h.element_size() * (min(E, T * top) * F * C + T * C + T * top * F))
     _check(library().nib_moe_up(_dt(h), _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), _ptr(inner), T, C, F, top,
-                                int(act), int(gated), _ptr(in_weights), _stream()), "moe_up")
+                                int(act), float(act_prm), int(gated), _ptr(in_weights), _stream()), "moe_up")
 
 
 def moe_down(inner: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: Optional[torch.Tensor],
@@ -1231,7 +1266,7 @@ def moe_scale(inner_all: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
 
 
 def moe_gate_scale(pre: torch.Tensor, inner_all: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor, T: int,
-                   n_expert: int, F: int, top: int, act: int, on_input: bool) -> None:
+                   n_expert: int, F: int, top: int, act: int, on_input: bool, act_prm: float = 0.0) -> None:
     """pre [T, n_expert * 2F] holds every expert's (gate, value) pairs; inner_all [T, n_expert * F] = act(s g) * (s u)
     (``on_input``) or s * act(g) * u, s the row's weight for the expert, 0 where the row did not choose it."""
     if not pre.is_contiguous() or not inner_all.is_contiguous() or pre.shape[1] != 2 * n_expert * F \
@@ -1241,12 +1276,12 @@ def moe_gate_scale(pre: torch.Tensor, inner_all: torch.Tensor, ids: torch.Tensor
         _note("other", "experts_gate", (T, n_expert * F, 0), 4.0 * T * n_expert * F,
               T * n_expert * F * (2.0 * pre.element_size() + inner_all.element_size()))
     _check(library().nib_moe_gate_scale(_dt(pre), _dt(inner_all), _ptr(pre), _ptr(inner_all), _ptr(ids), _ptr(weights),
-                                        T, n_expert, F, top, int(act), int(on_input), _stream()), "moe_gate_scale")
+                                        T, n_expert, F, top, int(act), float(act_prm), int(on_input), _stream()), "moe_gate_scale")
 
 
 def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: torch.Tensor, weights: torch.Tensor,
                 inner: torch.Tensor, x: torch.Tensor, T: int, top: int, act: int, workspace, gated: bool = False,
-                weight_on_input: bool = False) -> None:
+                weight_on_input: bool = False, act_prm: float = 0.0) -> None:
     """x[t] += sum_k weights[t, k] * W_down[ids[t, k]] . act(W_up[ids[t, k]] . h[t]) with w_up [experts, F, C] and
     w_down [experts, C, F].  Steps of few rows: row by row.  Steps of many rows: all experts through the engine's
     own products with the unchosen ones scaled to zero in between (``moe_dense_pays``: the first matrices as one
@@ -1270,7 +1305,7 @@ def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: 
         if gated:
             pre = workspace.get("moe.pre_all", (x.shape[0], E * 2 * F), torch.float32)
             linear(h, w_up.view(E * 2 * F, C), None, pre, T)
-            moe_gate_scale(pre, inner_all, ids, weights, T, E, F, top, act, weight_on_input)
+            moe_gate_scale(pre, inner_all, ids, weights, T, E, F, top, act, weight_on_input, act_prm)
         else:
             linear(h, w_up.view(E * F, C), None, inner_all, T, act=act)
             moe_scale(inner_all, ids, weights, T, E, F, top)
@@ -1282,7 +1317,7 @@ def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: 
     fits = all(32 * (K + 2) * es + 4 * K * 16 <= 200 * 1024 for K in (C, F))   # a tile of 32 outputs, four rows a warp
     grouped = MOE_GROUPED and T * top >= MOE_GROUPED_MIN_ROWS_PER_EXPERT * E and fits
     if not grouped:
-        moe_up(h, w_up, ids, inner, T, top, act, gated, in_w)
+        moe_up(h, w_up, ids, inner, T, top, act, gated, in_w, act_prm)
         moe_down(inner, w_down, ids, out_w, x, T, top)
         return
     _f32(x, "moe_experts: x")
@@ -1295,19 +1330,19 @@ def moe_experts(h: torch.Tensor, w_up: torch.Tensor, w_down: torch.Tensor, ids: 
               h.element_size() * (min(E, T * top) * F * C + T * C + T * top * F))
     if gated:
         _check(lib.nib_moe_grouped(dt, 3, _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), _ptr(in_w), _ptr(inner), None, T,
-                                   top, E, 2 * F, C, int(act), _stream()), "moe_grouped gated up")
+                                   top, E, 2 * F, C, int(act), float(act_prm), _stream()), "moe_grouped gated up")
     else:
         _check(lib.nib_moe_grouped(dt, 0, _ptr(h), h.stride(0), _ptr(w_up), _ptr(ids), None, _ptr(inner), None, T, top,
-                                   E, F, C, int(act), _stream()), "moe_grouped up")
+                                   E, F, C, int(act), 0.0, _stream()), "moe_grouped up")
     parts = workspace.get("moe.parts", (T * top, C), torch.float32)
     if tracing():
         _note("moe", "experts_down", (T * top, F, C), 2.0 * T * top * C * F,
               h.element_size() * (min(E, T * top) * F * C + T * top * F) + 4.0 * T * top * C)
     _check(lib.nib_moe_grouped(dt, 1, _ptr(inner), inner.stride(0), _ptr(w_down), _ptr(ids), _ptr(out_w), _ptr(parts),
-                               None, T, top, E, C, F, 0, _stream()), "moe_grouped down")
+                               None, T, top, E, C, F, 0, 0.0, _stream()), "moe_grouped down")
     if tracing():
         _note("other", "experts_sum", (T, C, top), T * C * top, 4.0 * T * C * (top + 2))
-    _check(lib.nib_moe_grouped(dt, 2, _ptr(parts), 0, None, None, None, None, _ptr(x), T, top, E, C, F, 0, _stream()),
+    _check(lib.nib_moe_grouped(dt, 2, _ptr(parts), 0, None, _ptr(ids), None, None, _ptr(x), T, top, E, C, F, 0, 0.0, _stream()),
            "moe_grouped sum")
 
 
@@ -1481,22 +1516,28 @@ def _scan_padded_host(n: int) -> int:
 
 
 def short_conv(proj: torch.Tensor, c_off: int, channels: int, taps: int, w: torch.Tensor, bias: Optional[torch.Tensor],
-               state: torch.Tensor, ctx, out: torch.Tensor, act: int) -> None:
+               state: torch.Tensor, ctx, out: torch.Tensor, act: int, out16: Optional[torch.Tensor] = None) -> None:
     """out[t, c] = act(bias[c] + sum_j w[c, j] x[t - (taps - 1 - j), c]) over the columns c_off .. of the 32-bit
     ``proj``, per batch entry in row order; what lies before an entry's first row comes from the first
     (taps - 1) * channels floats of the request's row of ``state`` (oldest first), which then moves on by the
-    entry's rows.  A step in which every entry is one row does both in one launch."""
-    _f32(proj, "short_conv: proj"); _f32(state, "short_conv: state"); _f32(out, "short_conv: out"); _f32(w, "short_conv: w")
+    entry's rows.  A step in which every entry is one row does both in one launch.  ``out16`` (bfloat16, optional)
+    receives the same values once more, for a matrix product that reads them."""
+    _f32(proj, "short_conv: proj"); _f32(out, "short_conv: out"); _f32(w, "short_conv: w")
+    if state.dtype != torch.float32:       # (a view of some columns of the slots' rows will do)
+        raise KernelError("short_conv: state must be float32")
     if w.shape != (channels, taps) or not w.is_contiguous() or proj.stride(1) != 1 or out.stride(1) != 1 \
             or state.stride(1) != 1 or out.shape[1] < channels:
         raise KernelError("short_conv: w contiguous [channels, taps], rows of proj, out and state contiguous")
     T, E = ctx.n_rows, ctx.n_entries
+    if out16 is not None and (out16.dtype != torch.bfloat16 or out16.stride(1) != 1 or out16.shape[1] < channels):
+        raise KernelError("short_conv: out16 must be bfloat16 [rows, >= channels], rows contiguous")
     fused = int(T == E)      # (every entry has a row, so as many rows as entries means one each)
     if tracing():
         _note("other", "short_conv", (T, channels, taps), 2.0 * T * channels * taps, 8.0 * T * channels)
     _check(library().nib_short_conv(_ptr(proj), proj.stride(0), int(c_off), int(channels), int(taps), _ptr(w),
                                     _ptr(bias), _ptr(state), state.stride(0), _ptr(ctx.row_entry), _ptr(ctx.entry_start),
-                                    _ptr(ctx.entry_slot), _ptr(out), out.stride(0), T, E, int(act), fused, _stream()),
+                                    _ptr(ctx.entry_slot), _ptr(out), out.stride(0), T, E, int(act), fused, _ptr(out16),
+                                    out16.stride(0) if out16 is not None else 0, _stream()),
            "short_conv", 1 if fused or taps <= 1 else 2)
 
 
@@ -1522,7 +1563,9 @@ def gated_scan(delta: bool, cv: torch.Tensor, q_off: int, k_off: int, v_off: int
     state space: S <- a S + k (w v)^T; o = S^T q + skip[h] v.  ``cv`` holds the rows' vectors (q of key/query head g
     at q_off + g n, k at k_off + g n, v of head h at v_off + h v; head h reads key/query head h // kq_ratio);
     the matrices live at ``s_off`` floats into each request's row of ``state``; out [rows, n_head * v] float32."""
-    _f32(cv, "gated_scan: cv"); _f32(coef, "gated_scan: coef"); _f32(state, "gated_scan: state"); _f32(out, "gated_scan: out")
+    _f32(cv, "gated_scan: cv"); _f32(coef, "gated_scan: coef"); _f32(out, "gated_scan: out")
+    if state.dtype != torch.float32 or state.data_ptr() % 16:       # (a view of some columns of the slots' rows will do)
+        raise KernelError("gated_scan: state must be float32, 16-byte aligned")
     if state.stride(1) != 1 or cv.stride(1) != 1 or out.stride(1) != 1:
         raise KernelError("gated_scan: rows of cv, state and out must be contiguous")
     if tracing():
@@ -1552,3 +1595,143 @@ def gated_norm(o: torch.Tensor, gate: Optional[torch.Tensor], weight: torch.Tens
                                     _ptr(weight), weight.numel(), int(n_groups), int(group_size), float(eps),
                                     int(bool(gate_first)), float(out_scale), _ptr(out), out.stride(0), n_rows, _stream()),
            "gated_norm")
+
+
+# ----------------------------------------------------------------------------- rotary positions in the halves layout
+def wide_norm_rope_append(src: torch.Tensor, offsets, n_head: int, n_kv_head: int, dim: int, vdim: int,
+                          wq: Optional[torch.Tensor], wk: Optional[torch.Tensor], eps: float, rot_dims: int,
+                          freqs: Optional[torch.Tensor], ctx, q_out: torch.Tensor, cache: Optional[torch.Tensor],
+                          block_table: Optional[torch.Tensor]) -> None:
+    """From 32-bit rows ``src`` (q, k, v at the three column ``offsets``): queries and keys divided by the root mean
+    square of the WHOLE projection (all heads at once, ``eps`` inside the root) and multiplied by a weight of the
+    projection's size (``wq`` [n_head * dim], ``wk`` [n_kv_head * dim]; None: no norm), then turned by the rows'
+    positions in the halves layout (value i of a head's first ``rot_dims`` pairs with value i + rot_dims / 2), cast,
+    padded to the cache's head size and written: queries to ``q_out``, keys and values to the rows' cache slots.
+    The values are read as they stand; their offset may be the keys' own."""
+    _f32(src, "wide_norm_rope_append: src")
+    hd = q_out.shape[1] // n_head
+    if cache is not None:
+        n_pages, two, g, page_size, chd = cache.shape
+        if two != 2 or g != n_kv_head or chd != hd or not cache.is_contiguous() or cache.dtype != q_out.dtype:
+            raise KernelError("wide_norm_rope_append: cache must be contiguous [pages, 2, kv heads, page, head size] of "
+                              "q_out's dtype")
+        _i32(block_table, "block_table")
+    else:
+        n_pages, page_size = 0, 1
+    if (wq is not None and (wq.dtype != torch.float32 or wq.numel() != n_head * dim)) or \
+            (wk is not None and (wk.dtype != torch.float32 or wk.numel() != n_kv_head * dim)):
+        raise KernelError("wide_norm_rope_append: a norm weight must be float32 of the projection's size")
+    if freqs is not None and freqs.dtype != torch.float64:
+        raise KernelError("wide_norm_rope_append: freqs must be float64")
+    if tracing():
+        n = (n_head + 2 * n_kv_head) * hd
+        _note("kv_write", "norm_kv_write", (ctx.n_rows, n, 0), 8.0 * ctx.n_rows * n, ctx.n_rows * n * (4.0 + q_out.element_size()))
+    _check(library().nib_wide_norm_rope_append(
+        _dt(q_out), _ptr(src), src.stride(0), offsets[0], offsets[1], offsets[2], n_head, n_kv_head, dim, vdim, hd,
+        _ptr(wq), _ptr(wk), float(eps), rot_dims, _ptr(freqs), _ptr(ctx.positions), _ptr(ctx.row_entry), _ptr(q_out),
+        q_out.stride(0), _ptr(cache), _ptr(block_table), block_table.shape[1] if block_table is not None else 0,
+        page_size, n_pages, ctx.n_rows, _ptr(ctx.status), _stream()), "wide_norm_rope_append")
+
+
+def rope_halves(rows: torch.Tensor, q_off: int, k_off: int, n_head: int, dim: int, rot_dims: int,
+                freqs: Optional[torch.Tensor], positions: torch.Tensor, k_mul: float, n_rows: int,
+                decay: Optional[torch.Tensor] = None, coef: Optional[torch.Tensor] = None) -> None:
+    """In place on the 32-bit ``rows``: ``n_head`` query heads at ``q_off`` and as many key heads at ``k_off`` turned
+    by the rows' positions in the halves layout, the keys then times ``k_mul``.  With ``coef`` (float32
+    [rows, n_head, 2]): coef[t, h] = (decay[h], 1), the decays and strengths of a recurrence whose decay is fixed."""
+    _f32(rows, "rope_halves: rows")
+    _i32(positions, "positions")
+    if freqs is not None and freqs.dtype != torch.float64:
+        raise KernelError("rope_halves: freqs must be float64")
+    if coef is not None:
+        _f32(coef, "rope_halves: coef"); _f32(decay, "rope_halves: decay")
+        if decay.numel() != n_head:
+            raise KernelError("rope_halves: one decay per head")
+    if tracing():
+        _note("other", "rope", (n_rows, 2 * n_head * dim, 0), 6.0 * n_rows * n_head * dim, 16.0 * n_rows * n_head * dim)
+    _check(library().nib_rope_halves(_ptr(rows), rows.stride(0), int(q_off), int(k_off), int(n_head), int(dim),
+                                     int(rot_dims), _ptr(freqs), _ptr(positions), float(k_mul), _ptr(decay), _ptr(coef),
+                                     n_rows, _stream()), "rope_halves")
+
+
+# ----------------------------------------------------------------------------- hyper-connections
+def hyper_enter(x: torch.Tensor, streams: torch.Tensor, in_w: torch.Tensor, w_next: torch.Tensor, eps: float,
+                xn: torch.Tensor, n_rows: int) -> None:
+    """streams[s][:n] = x[:n] for every copy s, and the first sublayer's input xn = u / sqrt(mean(u^2) + eps) * w_next
+    with u = sum_s in_w[s] * streams[s]; x [rows, C] and streams [S, rows, C] are 32-bit."""
+    _f32(x, "hyper_enter: x"); _f32(streams, "hyper_enter: streams"); _f32(in_w, "hyper_enter: in_w"); _f32(w_next, "hyper_enter: w_next")
+    S, C = streams.shape[0], x.shape[1]
+    if streams.shape[2] != C or in_w.numel() != S or w_next.numel() != C or not xn.is_contiguous() or xn.shape[1] != C:
+        raise KernelError("hyper_enter: streams [S, rows, C], in_w [S], w_next [C], xn contiguous [rows, C]")
+    if tracing():
+        _note("ln", "hyper", (n_rows, C, S), 4.0 * n_rows * C, n_rows * C * (4.0 + 4.0 * S + xn.element_size()))
+    _check(library().nib_hyper_enter(_dt(xn), _ptr(x), _ptr(streams), streams.stride(0), S, _ptr(in_w), _ptr(w_next),
+                                     float(eps), _ptr(xn), n_rows, C, _stream()), "hyper_enter")
+
+
+def hyper_update(streams: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Tensor], mix: torch.Tensor,
+                 out_w: torch.Tensor, eps: float, n_rows: int, in_next: Optional[torch.Tensor] = None,
+                 w_next: Optional[torch.Tensor] = None, xn: Optional[torch.Tensor] = None,
+                 total: Optional[torch.Tensor] = None) -> None:
+    """A sublayer's result ``y`` (32-bit [rows, C], zeroed here for the next one) goes back into the S copies of the
+    stream: r = y * sigmoid(gate) (``gate`` None: r = y); streams[t] <- sum_s mix[s, t] streams[s] + out_w[t] r, all
+    copies at once from the old ones.  With ``xn``: the next sublayer's input, the norm (weight ``w_next``) of
+    sum_s in_next[s] streams[s], in xn's dtype.  ``total`` (32-bit [rows, C], optional) receives the copies' sum."""
+    _f32(streams, "hyper_update: streams"); _f32(y, "hyper_update: y"); _f32(mix, "hyper_update: mix"); _f32(out_w, "hyper_update: out_w")
+    S, C = streams.shape[0], y.shape[1]
+    if streams.shape[2] != C or mix.numel() != S * S or out_w.numel() != S:
+        raise KernelError("hyper_update: streams [S, rows, C], mix [S, S], out_w [S]")
+    if gate is not None and (gate.dtype != torch.float32 or gate.stride(1) != 1 or gate.shape[1] < C):
+        raise KernelError("hyper_update: gate must be float32 [rows, >= C], rows contiguous")
+    if xn is not None:
+        _f32(in_next, "hyper_update: in_next"); _f32(w_next, "hyper_update: w_next")
+        if in_next.numel() != S or w_next.numel() != C or not xn.is_contiguous() or xn.shape[1] != C:
+            raise KernelError("hyper_update: in_next [S], w_next [C], xn contiguous [rows, C]")
+    if total is not None:
+        _f32(total, "hyper_update: total")
+    if tracing():
+        _note("ln", "hyper", (n_rows, C, S), (6.0 + 2.0 * S * S) * n_rows * C,
+              n_rows * C * (8.0 + 8.0 * S + (4.0 if gate is not None else 0.0) + (xn.element_size() if xn is not None else 0)))
+    _check(library().nib_hyper_update(_dt(xn) if xn is not None else 0, _ptr(streams), streams.stride(0), S, _ptr(y),
+                                      _ptr(gate), gate.stride(0) if gate is not None else 0, _ptr(mix), _ptr(out_w),
+                                      _ptr(in_next) if xn is not None else None, _ptr(w_next) if xn is not None else None,
+                                      float(eps), _ptr(xn), _ptr(total), n_rows, C, _stream()), "hyper_update")
+
+
+# ----------------------------------------------------------------------------- the selective scan
+SSM_MAX_PER_LANE = 8
+
+
+def selective_scan_padded(n: int) -> int:
+    """The state size ``n`` rounded up to the lanes that share a channel (0: too large)."""
+    if n <= 0 or n > 32 * SSM_MAX_PER_LANE:
+        return 0
+    lanes = 1
+    while -(-n // lanes) > SSM_MAX_PER_LANE:
+        lanes *= 2
+    return -(-n // lanes) * lanes
+
+
+def selective_scan(dtp: torch.Tensor, x: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, z: torch.Tensor,
+                   A_log: torch.Tensor, D: torch.Tensor, state: torch.Tensor, s_off: int, ctx, inner: int, n: int,
+                   out: torch.Tensor) -> None:
+    """Mamba's recurrence over the step's rows, entry by entry in row order (csrc/selective_scan.cu): per channel c and
+    state index j, with dt = softplus(dtp):  S[c, j] <- exp(-dt_c exp(A_log[c, j])) S[c, j] + dt_c x_c B_j;
+    out_c = (sum_j S[c, j] C_j + D_c x_c) * silu(z_c).  ``dtp``, ``x``, ``z`` [rows, >= inner] and ``bc`` (B at
+    ``b_off``, C at ``c_off``) are 32-bit; the matrices [inner][selective_scan_padded(n)] live ``s_off`` floats into
+    each request's row of ``state``."""
+    for t, name in ((dtp, "dtp"), (x, "x"), (bc, "bc"), (z, "z"), (state, "state")):
+        if t.dtype != torch.float32 or t.stride(1) != 1:
+            raise KernelError(f"selective_scan: {name} must be float32 with contiguous rows")
+    _f32(A_log, "selective_scan: A_log"); _f32(D, "selective_scan: D")
+    if A_log.numel() != inner * n or D.numel() != inner or out.stride(1) != 1 or selective_scan_padded(n) == 0:
+        raise KernelError("selective_scan: A_log [inner, n], D [inner], n at most 256")
+    if tracing():
+        T = ctx.n_rows
+        _note("scan", "selective_scan", (T, inner, n), 9.0 * T * inner * n,
+              T * (inner * (12.0 + out.element_size()) + 8.0 * n) + 8.0 * ctx.n_entries * inner * n)
+    _check(library().nib_selective_scan(_dt(out), _ptr(dtp), dtp.stride(0), _ptr(x), x.stride(0), _ptr(bc), bc.stride(0),
+                                        int(b_off), int(c_off), _ptr(z), z.stride(0), _ptr(A_log), _ptr(D), _ptr(state),
+                                        state.stride(0), int(s_off), _ptr(ctx.entry_start), _ptr(ctx.entry_slot),
+                                        ctx.n_entries, int(inner), int(n), _ptr(out), out.stride(0), _stream()),
+           "selective_scan")

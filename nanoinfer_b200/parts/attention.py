@@ -387,3 +387,131 @@ class NormedAttention(GeneralAttention):
                       sink=self.sink, extras=extras)
         ops.trace_scope(ctx.layer, "attn_proj")
         ops.linear(att, self.w_out, self.out_bias, x, T, residual=True)
+
+
+@register_mixer("span_attention")
+class SpanAttention(GeneralAttention):
+    """Attention whose queries see only the keys of their own span of ``span`` positions (position i sees j <= i with
+    i // span == j // span; spans count from position 0 of the sequence, however a prompt is cut into steps; 0: all
+    keys), with what this kind of layer puts around it, each an option:
+
+    * ``taps`` > 0: a short causal convolution over time on every channel of q and of k (weights [channels, taps],
+      the last tap the current token's, zeros before the sequence, no bias), right behind the projection; the last
+      ``taps - 1`` projected rows of a request are its state;
+    * ``wide_norm``: q and k are each divided by the root mean square of the WHOLE projection (all heads at once)
+      and multiplied by a weight of that size, ahead of the rotation;
+    * ``rot_dims``/``rot_base``: rotary positions in the halves layout on the first ``rot_dims`` values of a head;
+    * ``values_are_keys``: there is no value projection; a key head as it leaves the convolution (ahead of norm and
+      rotation) is the value head (so ``v_dim`` equals ``head_dim``);
+    * ``head_temperature``: a learned number per query head that multiplies the scale;
+    * ``learned_sink``: a learned number per query head whose exponential joins the softmax's denominator (a key
+      without a value, neither scaled nor multiplied by the temperature).
+
+    One product makes [q | k (| v)] as 32-bit floats, one kernel the convolution (and its state), one the norm, the
+    rotation, the cast and the cache write; then the attention kernels with the span, the heads' scales and the sinks
+    as options, and the output projection."""
+
+    def __init__(self, width: int, n_head: int, n_kv_head: int, head_dim: int, v_dim: int, scale: float, eps: float,
+                 span: int = 0, taps: int = 0, wide_norm: bool = True, rot_dims: int = 0, rot_base: float = 10000.0,
+                 values_are_keys: bool = False, head_temperature: bool = False, learned_sink: bool = False,
+                 out_scale: float = 1.0):
+        from .base import POSITIONS
+
+        if values_are_keys and v_dim != head_dim:
+            raise ValueError("span_attention: values that are the keys have the keys' size")
+        if span < 0 or taps < 0 or rot_dims < 0 or rot_dims % 2 or rot_dims > head_dim:
+            raise ValueError("span_attention: span and taps must not be negative, rot_dims even and at most head_dim")
+        super().__init__(width, n_head, n_kv_head, head_dim, v_dim, scale, window=0, sink=learned_sink, position=None)
+        self.eps, self.span, self.taps, self.wide_norm = float(eps), int(span), int(taps), bool(wide_norm)
+        self.values_are_keys, self.head_temperature = bool(values_are_keys), bool(head_temperature)
+        self.learned_sink, self.out_scale = bool(learned_sink), float(out_scale)
+        self.rotary = POSITIONS.build("rotary_halves", base=rot_base, dims=rot_dims)
+        if self.values_are_keys:
+            self.n_v = 0
+        self.n_proj = _round_up(self.n_q + self.n_k + self.n_v, 8)
+        #: channels that pass the convolution (q and k), and the floats of state that keeps per request
+        self.channels = self.n_q + self.n_k
+        self.state_floats = _round_up(max(self.taps - 1, 0) * self.channels, 4)
+
+    capture_safe = True
+
+    def param_specs(self) -> List[ParamSpec]:
+        c = self.width
+        specs = [ParamSpec("q_weight", (self.n_q, c), MATRIX), ParamSpec("k_weight", (self.n_k, c), MATRIX),
+                 ParamSpec("out_weight", (c, self.n_head * self.v_dim), MATRIX)]
+        if not self.values_are_keys:
+            specs.append(ParamSpec("v_weight", (self.n_v, c), MATRIX))
+        if self.taps > 0:
+            specs += [ParamSpec("q_conv", (self.n_q, self.taps), VECTOR), ParamSpec("k_conv", (self.n_k, self.taps), VECTOR)]
+        if self.wide_norm:
+            specs += [ParamSpec("q_norm", (self.n_q,), VECTOR, INIT_ONE_PLUS_NORMAL),
+                      ParamSpec("k_norm", (self.n_k,), VECTOR, INIT_ONE_PLUS_NORMAL)]
+        if self.head_temperature:
+            specs.append(ParamSpec("temperature", (self.n_head,), VECTOR, INIT_ONE_PLUS_NORMAL))
+        if self.learned_sink:
+            specs.append(ParamSpec("sink", (self.n_head,), VECTOR))
+        return specs
+
+    def state_spec(self):
+        from .base import StateSpec
+
+        return StateSpec((self.state_floats,), torch.float32) if self.state_floats else None
+
+    def prepare(self, dtype, device) -> None:
+        Mixer.prepare(self, dtype, device)
+        self.rotary.prepare(dtype, device)
+        p = self.params
+        q = p["q_weight"]
+        w = torch.zeros(self.n_proj, self.width, dtype=q.dtype, device=q.device)
+        at = 0
+        for key in ("q_weight", "k_weight") + (() if self.values_are_keys else ("v_weight",)):
+            n = p[key].shape[0]
+            w[at:at + n] = p[key]
+            p[key] = w[at:at + n]
+            at += n
+        self.w_qkv = w
+        self._pad_out_weight()
+        if self.out_scale != 1.0:
+            self.w_out = self.w_out * self.out_scale
+        self.conv_w = torch.cat([p["q_conv"], p["k_conv"]], 0).contiguous() if self.taps > 0 else None
+
+    def reserve(self, workspace: Workspace, limits: StepLimits) -> None:
+        super().reserve(workspace, limits)
+        workspace.reserve("attention.conv32", limits.max_rows * _round_up(self.channels, 4), torch.float32)
+
+    def forward(self, xn: torch.Tensor, x: torch.Tensor, ctx: StepContext, cache: Optional[KVCacheView],
+                state: Optional[torch.Tensor], writes_cache: bool = True) -> None:
+        if cache is None or not writes_cache:
+            raise ValueError("span_attention needs a paged cache of its own")
+        if self.state_floats and state is None:
+            raise ValueError("span_attention: the convolution needs a state slot tensor")
+        if isinstance(xn, ops.NormInput):
+            xn = xn.materialise(ctx.n_rows)
+        T, ws, p = ctx.n_rows, ctx.workspace, self.params
+        proj = ws.get("attention.proj32", (ctx.max_rows, self.n_proj), torch.float32)
+        ops.trace_scope(ctx.layer, "qkv")
+        ops.linear(xn, self.w_qkv, None, proj, T)
+        src, k_off = proj, self.n_q
+        if self.taps > 0:
+            src = ws.get("attention.conv32", (ctx.max_rows, _round_up(self.channels, 4)), torch.float32)
+            ops.short_conv(proj, 0, self.channels, self.taps, self.conv_w, None, state, ctx, src, ops.ACT_NONE)
+        # the values: the keys' own columns as they stand here, or the value projection's (which no convolution touches)
+        v_src_off = k_off if self.values_are_keys else None
+        q = ws.get("attention.q", (ctx.max_rows, self.q_dim), self.dtype)
+        if v_src_off is None:
+            if src is not proj:   # the value columns did not pass the convolution: they are read from the projection
+                raise NotImplementedError("span_attention: a value projection beside a convolution on q and k")
+            v_src_off = self.n_q + self.n_k
+        ops.wide_norm_rope_append(src, (0, k_off, v_src_off), self.n_head, self.n_kv_head, self.key_dim, self.v_dim,
+                                  p["q_norm"] if self.wide_norm else None, p["k_norm"] if self.wide_norm else None,
+                                  self.eps, self.rotary.dims, self.rotary.freqs, ctx, q, cache.layer, cache.block_table)
+        att = ws.get("attention.out", (ctx.max_rows, self.q_dim), self.dtype)
+        plan = ctx.plans.get("causal_attention")
+        if plan is None:
+            plan = ctx.plans["causal_attention"] = AttentionPlan(ctx.host_entry_start, ctx.host_entry_pos0,
+                                                                 device=x.device)
+        extras = ops.AttnExtras(span=self.span, head_scale=p.get("temperature"), sinks=p.get("sink"))
+        ops.attention(q, cache.layer, att, cache.block_table, ctx, self.n_head, self.scale, 0, plan,
+                      sink=self.learned_sink, extras=extras)
+        ops.trace_scope(ctx.layer, "attn_proj")
+        ops.linear(att, self.w_out, None, x, T, residual=True)

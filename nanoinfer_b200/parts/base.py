@@ -208,6 +208,12 @@ class DepthMix(Part):
     n_levels = 0
 
 
+class Connector(Part):
+    """How a sublayer's result goes back into the residual stream(s) where that takes parameters of its own (the
+    weights of several stream copies, a gate on the result).  The block arrangement that holds one applies it; the
+    part owns the parameters."""
+
+
 class FeedForward(Part):
     """Per-row transformation; ``forward`` ADDS its output to the residual stream ``x``.
     ``takes_norm_input`` as for mixers."""
@@ -262,6 +268,7 @@ FEED_FORWARDS = Registry("feed-forward")
 EMBEDDINGS = Registry("embedding")
 HEADS = Registry("head")
 DEPTH_MIXES = Registry("depth mix")
+CONNECTORS = Registry("connector")
 
 register_norm = NORMS.register
 register_position = POSITIONS.register
@@ -270,6 +277,7 @@ register_feed_forward = FEED_FORWARDS.register
 register_embedding = EMBEDDINGS.register
 register_head = HEADS.register
 register_depth_mix = DEPTH_MIXES.register
+register_connector = CONNECTORS.register
 
 
 # ----------------------------------------------------------------------------- what a step shows to the parts

@@ -11,7 +11,7 @@ from typing import Callable, ClassVar, Dict, Optional, Type
 import torch
 
 from ..kernels import ops
-from .base import (DEPTH_MIXES, FEED_FORWARDS, MIXERS, NORMS, KVCacheView, Mixer, Part, Registry, StepContext,
+from .base import (CONNECTORS, DEPTH_MIXES, FEED_FORWARDS, MIXERS, NORMS, KVCacheView, Mixer, Part, Registry, StepContext,
                    StepLimits, Workspace)
 
 BLOCKS: Dict[str, Type["Block"]] = {}
@@ -249,5 +249,83 @@ class OutputNormBlock(Block):
                 part.forward(xn, y, ctx)
             last = i + 1 == len(self.sublayers)
             ops.add_norm(x, y, norm.params["weight"], self.eps, T, None, None if last and not fuse else xn)
+        if fuse:
+            ctx.stream_entered = True
+
+
+@register_block("hyper_connections")
+class HyperConnectionBlock(Block):
+    """Pre-norm sublayers on several copies of the residual stream (hyper-connections):
+        u = sum_s in[s] x_s;   y = sublayer(norm(u));   x_t <- sum_s mix[s, t] x_s + out[t] y   for all copies t at once
+    for the mixer (``norm_1``, ``connect_1``) and then for the feed-forward (``norm_2``, ``connect_2``; a layer may have
+    none).  A connector that is ``gated`` multiplies y by sigmoid(W norm(u) + b) first.  The norms are RMS norms.  The
+    copies are all equal to the stream the first such layer is given; behind the last one the stream is their sum.
+
+    The copies live in a 32-bit buffer of the arrangement's own.  A sublayer adds its products into a 32-bit buffer
+    that it finds zero; the gate's logits are one more product of the sublayer's input.  Between two sublayers runs ONE
+    kernel: the gate, all copies' update, the buffer zeroed again, and the next sublayer's normed input, also the next
+    layer's where that is of this arrangement (``ctx.stream_entered`` tells it that its input is ready); behind the
+    last layer of the arrangement the same kernel leaves the copies' sum in the stream."""
+
+    slots = {"norm_1": NORMS, "mixer": MIXERS, "connect_1": CONNECTORS, "norm_2": NORMS, "feed_forward": FEED_FORWARDS,
+             "connect_2": CONNECTORS}
+    optional = ("norm_2", "feed_forward", "connect_2")
+    #: True: every layer also leaves the copies' sum in the stream (for looking at a model layer by layer)
+    always_sum = False
+
+    def __init__(self, width: int, parts: Dict[str, Part]):
+        super().__init__(width, parts)
+        have = [name in parts for name in ("norm_2", "feed_forward", "connect_2")]
+        if any(have) and not all(have):
+            raise ValueError("hyper_connections: norm_2, feed_forward and connect_2 come together or not at all")
+        norms = [parts[n] for n in ("norm_1", "norm_2") if n in parts]
+        if any(not hasattr(n, "eps") or "bias" in {s.key for s in n.param_specs()} for n in norms):
+            raise ValueError("hyper_connections: its norms must be RMS norms")
+        self.norm_2, self.feed_forward, self.connect_2 = parts.get("norm_2"), parts.get("feed_forward"), parts.get("connect_2")
+        connectors = [parts[n] for n in ("connect_1", "connect_2") if n in parts]
+        if len({c.streams for c in connectors}) != 1 or any(c.width != self.width for c in connectors):
+            raise ValueError("hyper_connections: the connectors of a layer share the number of copies and the width")
+        self.streams = connectors[0].streams
+
+    def reserve(self, workspace, limits) -> None:
+        workspace.reserve("block.normed", limits.max_rows * self.width, limits.dtype)
+        workspace.reserve("block.sublayer", limits.max_rows * self.width, torch.float32, zeroed=True)
+        workspace.reserve("block.copies", self.streams * limits.max_rows * self.width, torch.float32)
+        workspace.reserve("block.gate", limits.max_rows * self.width, torch.float32)
+
+    def _back(self, connect, xn, y, copies, gate, ctx, T, nxt_norm, nxt_connect, total) -> None:
+        """The sublayer's result back into the copies, and the next sublayer's input (``nxt_norm`` None: none)."""
+        p = connect.params
+        if connect.gated:
+            ops.trace_scope(ctx.layer, "gate")
+            ops.linear(xn, p["gate_weight"], p["gate_bias"], gate, T)
+        ops.hyper_update(copies, y, gate if connect.gated else None, p["mix"], p["out"],
+                         nxt_norm.eps if nxt_norm is not None else 0.0, T,
+                         in_next=nxt_connect.params["in"] if nxt_norm is not None else None,
+                         w_next=nxt_norm.params["weight"] if nxt_norm is not None else None,
+                         xn=xn if nxt_norm is not None else None, total=total)
+
+    def forward(self, x, ctx, cache, state, writes_cache, dtype) -> None:
+        T, ws = ctx.n_rows, ctx.workspace
+        xn = ws.get("block.normed", (ctx.max_rows, self.width), dtype)
+        # zero when first handed out, and zeroed again by every kernel that reads it
+        y = ws.get_zeroed("block.sublayer", (ctx.max_rows, self.width), torch.float32)
+        copies = ws.get("block.copies", (self.streams, ctx.max_rows, self.width), torch.float32)
+        gate = ws.get("block.gate", (ctx.max_rows, self.width), torch.float32)
+        if ctx.stream_entered:
+            ctx.stream_entered = False      # the arrangement before this one left the copies and norm_1's output behind
+        else:
+            ops.hyper_enter(x, copies, self.connect_1.params["in"], self.norm_1.params["weight"], self.norm_1.eps, xn, T)
+        nxt = ctx.next_block
+        fuse = isinstance(nxt, HyperConnectionBlock) and nxt.width == self.width and nxt.streams == self.streams
+        total = x if (not fuse or self.always_sum) else None
+        last = (nxt.norm_1, nxt.connect_1) if fuse else (None, None)
+        self.mixer.forward(xn, y, ctx, cache, state, writes_cache)
+        if self.feed_forward is None:
+            self._back(self.connect_1, xn, y, copies, gate, ctx, T, last[0], last[1], total)
+        else:
+            self._back(self.connect_1, xn, y, copies, gate, ctx, T, self.norm_2, self.connect_2, None)
+            self.feed_forward.forward(xn, y, ctx)
+            self._back(self.connect_2, xn, y, copies, gate, ctx, T, last[0], last[1], total)
         if fuse:
             ctx.stream_entered = True

@@ -202,49 +202,76 @@ class StateSpaceDuality(_ScanMixer):
 
 @register_mixer("parallel")
 class ParallelMixers(Mixer):
-    """Two mixers side by side that read the same input; the result is left_scale * left + right_scale * right.
+    """Two mixers side by side that read the same input.  The result is left_scale * left + right_scale * right or,
+    with ``out_norm_eps`` given, left_scale * norm(left) + right_scale * norm(right), each an RMS norm over the model
+    width with a weight of its own (``left.out_norm``, ``right.out_norm``).
     ``left`` and ``right`` are {"kind": registered name, "args": constructor arguments}; both kinds must take an
-    ``out_scale`` argument (the scale is applied inside each, ahead of its output projection, whose epilogue then adds
-    into the same buffer).  At most one of the two may want paged keys and values and at most one per-request state:
-    the cache manager gives a run of a layer one set of pages and one state tensor.  Parameters are named
-    ``left.<key>`` and ``right.<key>``."""
+    ``out_scale`` argument (without the norms the scale is applied inside each, ahead of its output projection, whose
+    epilogue then adds into the same buffer; with them each adds into a 32-bit buffer of its own that it finds zero,
+    and one kernel per side norms it, scales it, adds it to the result and zeroes it again).  At most one of the two
+    may want paged keys and values: the cache manager gives a run of a layer one set of pages.  Both may keep
+    per-request state: the layer's state row is the two side by side, each a multiple of four floats.  Parameters are
+    named ``left.<key>`` and ``right.<key>``."""
 
-    def __init__(self, width: int, left: dict, right: dict, left_scale: float = 1.0, right_scale: float = 1.0):
+    def __init__(self, width: int, left: dict, right: dict, left_scale: float = 1.0, right_scale: float = 1.0,
+                 out_norm_eps: Optional[float] = None):
         from .base import MIXERS
 
         self.width = int(width)
         self.left_scale, self.right_scale = float(left_scale), float(right_scale)
+        self.out_norm_eps = None if out_norm_eps is None else float(out_norm_eps)
+        inner = (1.0, 1.0) if self.out_norm_eps is not None else (self.left_scale, self.right_scale)
         self.children = {
-            "left": MIXERS.build(left["kind"], **{**left["args"], "out_scale": self.left_scale}),
-            "right": MIXERS.build(right["kind"], **{**right["args"], "out_scale": self.right_scale}),
+            "left": MIXERS.build(left["kind"], **{**left["args"], "out_scale": inner[0]}),
+            "right": MIXERS.build(right["kind"], **{**right["args"], "out_scale": inner[1]}),
         }
-        if sum(c.kv_spec() is not None for c in self.children.values()) > 1 or \
-                sum(c.state_spec() is not None for c in self.children.values()) > 1:
-            raise ValueError("parallel: at most one of the two mixers may want a paged cache, and at most one state")
+        if sum(c.kv_spec() is not None for c in self.children.values()) > 1:
+            raise ValueError("parallel: at most one of the two mixers may want a paged cache")
+        #: where each side's state lies in the layer's state row: side -> (first float, floats)
+        self.state_at, at = {}, 0
+        for side, c in self.children.items():
+            spec = c.state_spec()
+            if spec is not None:
+                if len(spec.shape) != 1 or spec.dtype != torch.float32:
+                    raise ValueError("parallel: a side's state must be one row of 32-bit floats")
+                self.state_at[side] = (at, int(spec.shape[0]))
+                at += _round_up(int(spec.shape[0]), 4)
+        self.state_floats = at
 
     def param_specs(self) -> List[ParamSpec]:
-        return [ParamSpec(f"{side}.{s.key}", s.shape, s.kind, s.init) for side, c in self.children.items()
-                for s in c.param_specs()]
+        specs = [ParamSpec(f"{side}.{s.key}", s.shape, s.kind, s.init) for side, c in self.children.items()
+                 for s in c.param_specs()]
+        if self.out_norm_eps is not None:
+            specs += [ParamSpec(f"{side}.out_norm", (self.width,), VECTOR, INIT_ONE_PLUS_NORMAL) for side in self.children]
+        return specs
 
     def bind(self, params) -> None:
         self.params = params
         for side, c in self.children.items():
-            c.bind({k[len(side) + 1:]: v for k, v in params.items() if k.startswith(side + ".")})
+            c.bind({k[len(side) + 1:]: v for k, v in params.items() if k.startswith(side + ".") and
+                    not (self.out_norm_eps is not None and k == side + ".out_norm")})
 
     def prepare(self, dtype, device) -> None:
         super().prepare(dtype, device)
         for c in self.children.values():
             c.prepare(dtype, device)
+        if self.out_norm_eps is not None:
+            # (the side's share of the sum rides in its norm's weight)
+            self.norm_w = {side: (self.params[f"{side}.out_norm"] * scale).contiguous()
+                           for side, scale in (("left", self.left_scale), ("right", self.right_scale))}
 
     def reserve(self, workspace: Workspace, limits: StepLimits) -> None:
         for c in self.children.values():
             c.reserve(workspace, limits)
+        if self.out_norm_eps is not None:
+            for side in self.children:
+                workspace.reserve(f"parallel.{side}", limits.max_rows * self.width, torch.float32, zeroed=True)
 
     def kv_spec(self):
         return next((c.kv_spec() for c in self.children.values() if c.kv_spec() is not None), None)
 
     def state_spec(self):
-        return next((c.state_spec() for c in self.children.values() if c.state_spec() is not None), None)
+        return StateSpec((self.state_floats,), torch.float32) if self.state_floats else None
 
     def step_planner(self):
         return next((c.step_planner() for c in self.children.values() if c.step_planner() is not None), None)
@@ -263,6 +290,15 @@ class ParallelMixers(Mixer):
                 state: Optional[torch.Tensor], writes_cache: bool = True) -> None:
         if isinstance(xn, ops.NormInput):
             xn = xn.materialise(ctx.n_rows)
-        for c in self.children.values():
-            c.forward(xn, x, ctx, cache if c.kv_spec() is not None else None,
-                      state if c.state_spec() is not None else None, writes_cache)
+        for side, c in self.children.items():
+            own = None
+            if side in self.state_at:
+                at, n = self.state_at[side]
+                own = state[:, at:at + n]
+            into = x
+            if self.out_norm_eps is not None:
+                # zero when first handed out, and zeroed again by the kernel that reads it
+                into = ctx.workspace.get_zeroed(f"parallel.{side}", (ctx.max_rows, self.width), torch.float32)
+            c.forward(xn, into, ctx, cache if c.kv_spec() is not None else None, own, writes_cache)
+            if self.out_norm_eps is not None:
+                ops.add_norm(x, into, self.norm_w[side], self.out_norm_eps, ctx.n_rows)

@@ -59,3 +59,23 @@ class RMSNorm(Norm):
     def forward(self, x: torch.Tensor, out: torch.Tensor, n_rows: int,
                 rows: Optional[torch.Tensor] = None) -> None:
         ops.rmsnorm(x, self.params["weight"], self.eps, out, n_rows, rows)
+
+
+@register_norm("scalar_rmsnorm")
+class ScalarRMSNorm(RMSNorm):
+    """An RMS norm whose weight is ONE number for all coordinates: x / sqrt(mean(x^2) + eps) * g.  The checkpoint's
+    tensor is a scalar; after loading it is spread over the width, so that every kernel that takes an RMS norm's
+    weight takes this one too."""
+
+    def __init__(self, width: int, eps: float):
+        super().__init__(width, eps, one_plus=False)
+
+    def param_specs(self) -> List[ParamSpec]:
+        return [ParamSpec("weight", (), VECTOR, INIT_ONE_PLUS_NORMAL)]
+
+    def prepare(self, dtype, device) -> None:
+        super().prepare(dtype, device)
+        w = self.params["weight"]
+        if w.numel() == 1:
+            self.scalar = w.reshape(())
+            self.params["weight"] = w.reshape(1).expand(self.width).contiguous()

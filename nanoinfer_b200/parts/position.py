@@ -73,3 +73,12 @@ class SinusoidalPositions(PositionEncoding):
 
     def on_embedding(self, x, ctx) -> None:
         ops.add_sinusoid(x, ctx.positions, self.freqs, ctx.n_rows)
+
+
+@register_position("rotary_halves")
+class RotaryHalves(RotaryPairs):
+    """Rotary positions in the halves layout: of every query and key head the first ``dims`` values turn, value i
+    paired with value i + dims / 2, by the angle position * base^(-2i / dims); the other values pass.  The rotation is
+    done by the mixer's own kernel (``kernels.ops.wide_norm_rope_append``, ``kernels.ops.rope_halves``)."""
+
+    layout = "halves"

@@ -12,7 +12,11 @@ expert; gate and value rows are interleaved into one matrix at load, so that one
 ``weight_on`` "input": the score multiplies what the expert READS, out = sum_e expert_e(s_e h), which for these
 experts is not the same as scaling the output (the first product is linear, so the kernels scale its results
 before the activation); ``shared_row_gate``: the shared expert's output times sigmoid(w_sg . h), one number a row
-(its row rides in the shared expert's first product).
+(its row rides in the shared expert's first product); ``choice_bias``: a learned number per expert that is added
+to the scores for the CHOICE only (the weights stay the scores); ``n_identity`` > 0: the router has that many outputs
+more than there are experts with matrices, and a row that chooses one of them gets its own input back, times the
+score (the routing kernel adds it, the expert kernels skip the choice); activation "swiglu_capped" (gated experts):
+g' = min(g, act_limit), u' = clamp(u, -act_limit, act_limit), g' sigmoid(1.702 g') (u' + 1).
 """
 from __future__ import annotations
 
@@ -22,7 +26,7 @@ from typing import List, Optional
 import torch
 
 from ..kernels import ops
-from .base import MATRIX, FeedForward, ParamSpec, StepContext, register_feed_forward
+from .base import MATRIX, VECTOR, FeedForward, ParamSpec, StepContext, register_feed_forward
 
 
 _instances = itertools.count()
@@ -32,13 +36,21 @@ _instances = itertools.count()
 class RoutedExperts(FeedForward):
     def __init__(self, width: int, n_expert: int, top: int, inner: int, activation: str = "erf",
                  renorm: bool = False, shared_inner: int = 0, shared_activation: str = "erf",
-                 score: str = "softmax", gated: bool = False, weight_on: str = "output", shared_row_gate: bool = False):
-        if not 0 < top <= n_expert:
-            raise ValueError(f"routed_experts: top {top} must be between 1 and the number of experts {n_expert}")
+                 score: str = "softmax", gated: bool = False, weight_on: str = "output", shared_row_gate: bool = False,
+                 choice_bias: bool = False, n_identity: int = 0, act_limit: float = 0.0):
+        if n_identity < 0 or not 0 < top <= n_expert + n_identity:
+            raise ValueError(f"routed_experts: top {top} must be between 1 and the number of experts {n_expert} "
+                             f"(+ {n_identity} without matrices)")
         for a in (activation, shared_activation):
-            if a not in (("tanh", "erf", "relu2", "silu") if gated else ("tanh", "erf")):
+            if a not in (("tanh", "erf", "relu2", "silu", "swiglu_capped") if gated else ("tanh", "erf")):
                 raise ValueError(f"routed_experts: activation {a!r} is not one of 'tanh', 'erf' (gated experts: "
-                                 "also 'relu2', 'silu')")
+                                 "also 'relu2', 'silu', 'swiglu_capped')")
+        if activation == "swiglu_capped" and not act_limit > 0.0:
+            raise ValueError("routed_experts: 'swiglu_capped' needs a positive act_limit")
+        if shared_inner and shared_activation == "swiglu_capped":
+            raise ValueError("routed_experts: the shared expert does not take 'swiglu_capped'")
+        if n_identity and weight_on == "input":
+            raise ValueError("routed_experts: experts without matrices go with weights on the output")
         if score not in ("softmax", "sigmoid") or weight_on not in ("input", "output"):
             raise ValueError("routed_experts: score is 'softmax' or 'sigmoid', weight_on 'input' or 'output'")
         if weight_on == "input" and not gated:
@@ -54,9 +66,14 @@ class RoutedExperts(FeedForward):
         self._ids_name = f"moe.ids.{next(_instances)}"
         self.last_ids: Optional[torch.Tensor] = None
         self.shared_row_gate = bool(shared_row_gate)
+        self.choice_bias, self.n_identity, self.act_limit = bool(choice_bias), int(n_identity), float(act_limit)
+        #: outputs of the router: the experts with matrices, then those without
+        self.n_routes = self.n_expert + self.n_identity
 
     def param_specs(self) -> List[ParamSpec]:
-        specs = [ParamSpec("router", (self.n_expert, self.width), MATRIX)]
+        specs = [ParamSpec("router", (self.n_routes, self.width), MATRIX)]
+        if self.choice_bias:
+            specs.append(ParamSpec("choice_bias", (self.n_routes,), VECTOR))
         for e in range(self.n_expert):
             if self.gated:
                 specs.append(ParamSpec(f"expert{e}_gate", (self.inner, self.width), MATRIX))
@@ -74,7 +91,7 @@ class RoutedExperts(FeedForward):
     def matrix_flops_per_row(self) -> float:
         n_mat = 3 if self.gated else 2
         per_expert = 2.0 * n_mat * self.inner * self.width
-        return 2.0 * self.n_expert * self.width + self.top * per_expert + 2.0 * n_mat * self.shared_inner * self.width
+        return 2.0 * self.n_routes * self.width + self.top * per_expert + 2.0 * n_mat * self.shared_inner * self.width
 
     def prepare(self, dtype, device) -> None:
         super().prepare(dtype, device)
@@ -130,11 +147,13 @@ class RoutedExperts(FeedForward):
         ids = self.last_ids = ws.get(self._ids_name, (n, self.top), torch.int32)
         weights = ws.get("moe.weights", (n, self.top), torch.float32)
         ops.trace_scope(ctx.layer, "router")
-        ops.moe_route(xn, p["router"], T, self.top, self.renorm, ids, weights, score=self.score)
+        ops.moe_route(xn, p["router"], T, self.top, self.renorm, ids, weights, score=self.score,
+                      choice_bias=p.get("choice_bias"), n_real=self.n_expert, x=x)
         inner = ws.get("moe.inner", (n * self.top, self.inner), self.dtype)
         ops.trace_scope(ctx.layer, "experts")
         ops.moe_experts(xn, self.w_up, self.w_down, ids, weights, inner, x, T, self.top,
-                        ops.ACT_CODES[self.activation], ws, gated=self.gated, weight_on_input=self.weight_on == "input")
+                        ops.ACT_CODES[self.activation], ws, gated=self.gated, weight_on_input=self.weight_on == "input",
+                        act_prm=self.act_limit)
         if self.shared_inner:
             hs = ws.get("moe.shared", (n, self.shared_inner), self.dtype)
             ops.trace_scope(ctx.layer, "shared_fc")

@@ -86,5 +86,10 @@ def _register_builtin() -> None:
 
     register_architecture("Kemuzen", KemuzenConfig, build_kemuzen_spec)
 
+    from .config.nagilix import NagilixConfig
+    from .models.nagilix import build_nagilix_spec
+
+    register_architecture("Nagilix", NagilixConfig, build_nagilix_spec)
+
 
 _register_builtin()
