@@ -84,7 +84,10 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
   const int pos_first = entry_pos0[e] + q_off;           // position of the tile's first row
   const int pos_last = pos_first + n_rows - 1;
   const int* table = block_table + (size_t)e * max_blocks;
-  const int key_lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+  const int span = EX ? ex.span : 0;        // > 0: a row sees the keys of its own span of positions only
+  int key_lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+  if (span > 0) key_lo = max(key_lo, pos_first - pos_first % span);   // (the first row's span begins first)
+  if (EX && ex.head_scale) scale *= ex.head_scale[h];
   const int tile_first = key_lo / PF_BN, tile_last = pos_last / PF_BN;
   // keys 0 .. keep - 1 stay visible behind the window: their tiles, those ahead of the window's first, come first
   const int keep = EX && window > 0 ? ex.keep_first : 0;
@@ -134,8 +137,12 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
   const int rg = warp & 3, kh = warp >> 2;                  // row group and part of the keys
   const int r0 = rg * 16 + (lane >> 2), r1 = r0 + 8;        // rows within the tile
   const int p0 = pos_first + r0, p1 = pos_first + r1;       // their positions
-  const int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
-  const int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
+  int lo0 = (window > 0 && p0 - window + 1 > 0) ? p0 - window + 1 : 0;
+  int lo1 = (window > 0 && p1 - window + 1 > 0) ? p1 - window + 1 : 0;
+  if (span > 0) {
+    lo0 = max(lo0, p0 - p0 % span);
+    lo1 = max(lo1, p1 - p1 % span);
+  }
   uint32_t qf[HD / 16][4];
   constexpr float LOG2E = 1.4426950408889634f;
   const float scale2 = EX ? 1.0f : scale * LOG2E;   // (with EX the scores are brought to their final form first)
@@ -175,7 +182,7 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
     // powers of two; only the tiles on the causal edge (or a window's edge) need the mask.
     const int wp0 = pos_first + rg * 16, wp1 = wp0 + 15;     // positions of the warp's rows
     const int wj0 = tile * PF_BN + kh * PF_WN;               // the warp's first key of the tile
-    const bool edge = wj0 + PF_WN - 1 > wp0 || (window > 0 && wj0 < wp1 - window + 1);
+    const bool edge = wj0 + PF_WN - 1 > wp0 || (window > 0 && wj0 < wp1 - window + 1) || (span > 0 && wj0 < wp1 - wp1 % span);
     const int j_base = wj0 + (lane & 3) * 2;
     if (EX) {
       // the score in its final form, times log2(e): scale, cap, distance bias
@@ -280,8 +287,9 @@ attention_prefill_kernel(const bf16* q, int ldq, const bf16* cache, bf16* out,
     l0 = l0 * a0 + other.z * b0;
     l1 = l1 * a1 + other.w * b1;
     if (sink) {   // one more term in the denominator: a key of score 0 that has no value
-      if (mn0 != -INFINITY) l0 += pow2(-mn0);
-      if (mn1 != -INFINITY) l1 += pow2(-mn1);
+      const float sink2 = EX && ex.sinks ? ex.sinks[h] * 1.4426950408889634f : 0.0f;   // (exp(0) unless the heads have logits)
+      if (mn0 != -INFINITY) l0 += pow2(sink2 - mn0);
+      if (mn1 != -INFINITY) l1 += pow2(sink2 - mn1);
     }
 #pragma unroll
     for (int i = 0; i < HD / 8; ++i) {
@@ -352,9 +360,10 @@ extern "C" int nib_attention_prefill(const void* q, int ldq, const void* cache, 
                                      const float* gate, int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   const AttnExtras ex = {softcap, keep_first, slopes, gate, ldg, out_scale, span, head_scale, sinks};
-  const bool plain = !(softcap > 0.0f) && (keep_first <= 0 || window <= 0) && !slopes && !gate && out_scale == 1.0f;
+  const bool plain = !(softcap > 0.0f) && (keep_first <= 0 || window <= 0) && !slopes && !gate && out_scale == 1.0f &&
+                     span <= 0 && !head_scale && !sinks;
+  if (span < 0) return NIB_ERR_BAD_ARGUMENT;
   if (softcap < 0.0f || keep_first < 0) return NIB_ERR_BAD_ARGUMENT;
-  if (span > 0 || head_scale != nullptr || sinks != nullptr) return NIB_ERR_UNSUPPORTED_SIZE;
   if (!nib_attention_prefill_supported(head_dim)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f)) return NIB_ERR_BAD_ARGUMENT;
   if ((ldq & 7) || ((uintptr_t)q & 15) || (ldo & 1) || ((uintptr_t)out & 3)) return NIB_ERR_UNSUPPORTED_SIZE;

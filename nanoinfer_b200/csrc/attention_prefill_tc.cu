@@ -138,7 +138,9 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
   const int pos_last = pos_first + n_rows - 1;
   const int* table = prm.block_table + (size_t)e * prm.max_blocks;
   const int window = prm.window;
-  const int key_lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+  const int span = EX ? prm.ex.span : 0;    // > 0: a row sees the keys of its own span of positions only
+  int key_lo = (window > 0 && pos_first - window + 1 > 0) ? pos_first - window + 1 : 0;
+  if (span > 0) key_lo = max(key_lo, pos_first - pos_first % span);   // (the first row's span begins first)
   const int tile_first = key_lo / AT_BN, tile_last = pos_last / AT_BN;
   // keys 0 .. keep - 1 stay visible behind the window: their tiles, those ahead of the window's first, come first
   const int keep = EX && window > 0 ? prm.ex.keep_first : 0;
@@ -261,14 +263,16 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     const int r = quarter * 32 + lane;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quarter * 32) << 16);
     const int p = pos_first + r;
-    const int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    int lo = (window > 0 && p - window + 1 > 0) ? p - window + 1 : 0;
+    if (span > 0) lo = max(lo, p - p % span);
     const int wp0 = pos_first + quarter * 32, wp1 = wp0 + 31;   // positions of the warp's rows
     constexpr float LOG2E = 1.4426950408889634f;
-    const float scale2 = EX ? 1.0f : prm.scale * LOG2E;   // (with EX the scores are brought to their final form first)
+    const float scale_h = EX && prm.ex.head_scale ? prm.scale * prm.ex.head_scale[h] : prm.scale;
+    const float scale2 = EX ? 1.0f : scale_h * LOG2E;   // (with EX the scores are brought to their final form first)
     const float slope2 = EX && prm.ex.slopes ? prm.ex.slopes[h] * LOG2E : 0.0f;
     const float cap2 = EX ? prm.ex.softcap * LOG2E : 0.0f;
-    const float cap_in = EX && prm.ex.softcap > 0.0f ? 2.0f * LOG2E * prm.scale / prm.ex.softcap : 0.0f;
-    const float mul2 = prm.scale * LOG2E;
+    const float cap_in = EX && prm.ex.softcap > 0.0f ? 2.0f * LOG2E * scale_h / prm.ex.softcap : 0.0f;
+    const float mul2 = scale_h * LOG2E;
     float m = -INFINITY, l = 0.0f;
     bool ok = true;
     for (int it = 0; it < n_it; ++it) {
@@ -277,7 +281,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
       if (!ok) break;
       tc_fence_after();
       const int j0 = tile_of(it) * AT_BN;
-      const bool edge = j0 + AT_BN - 1 > wp0 || (window > 0 && j0 < wp1 - window + 1);   // only these tiles need the mask
+      const bool edge = j0 + AT_BN - 1 > wp0 || (window > 0 && j0 < wp1 - window + 1) ||
+                        (span > 0 && j0 < wp1 - wp1 % span);   // only these tiles need the mask
       float v[AT_BN];
 #pragma unroll
       for (int c = 0; c < AT_BN / 32; ++c) tmem_ld32(lane_addr + (uint32_t)(b * AT_BN + c * 32), v + c * 32);
@@ -360,7 +365,8 @@ attention_prefill_tc_kernel(const __grid_constant__ CUtensorMap map_q, const __g
     if (ok) ok = warp_mbar_wait(&o_full[(n_it - 1) % AT_NBUF], ((n_it - 1) / AT_NBUF) & 1, abort_flag, lane);
     if (ok) {
       tc_fence_after();
-      if (prm.sink && m != -INFINITY) l += at_pow2(-m);
+      // (the sink's term is exp(0) unless the heads have logits of their own)
+      if (prm.sink && m != -INFINITY) l += at_pow2((EX && prm.ex.sinks ? prm.ex.sinks[h] * LOG2E : 0.0f) - m);
       float inv = l > 0.0f ? 1.0f / l : 0.0f;
       if (EX) {
         inv *= prm.ex.out_scale;
@@ -410,8 +416,9 @@ extern "C" int nib_attention_prefill_tc(const void* q, int ldq, int T, const voi
                                         int ldg, float out_scale, int span, const float* head_scale, const float* sinks, int* status, cudaStream_t stream) {
   if (n_tiles <= 0) return 0;
   if (softcap < 0.0f || keep_first < 0) return NIB_ERR_BAD_ARGUMENT;
-  if (span > 0 || head_scale != nullptr || sinks != nullptr) return NIB_ERR_UNSUPPORTED_SIZE;
-  const bool plain = !(softcap > 0.0f) && (keep_first <= 0 || window <= 0) && !slopes && !gate && out_scale == 1.0f;
+  const bool plain = !(softcap > 0.0f) && (keep_first <= 0 || window <= 0) && !slopes && !gate && out_scale == 1.0f &&
+                     span <= 0 && !head_scale && !sinks;
+  if (span < 0) return NIB_ERR_BAD_ARGUMENT;
   if (!nib_attention_prefill_tc_supported(head_dim, page_size)) return NIB_ERR_UNSUPPORTED_SIZE;
   if (n_kv_head <= 0 || n_head % n_kv_head != 0 || !(scale > 0.0f) || T <= 0) return NIB_ERR_BAD_ARGUMENT;
   if ((ldq & 7) || ((uintptr_t)q & 15) || (ldo & 7) || ((uintptr_t)out & 15) || ((uintptr_t)cache & 15))

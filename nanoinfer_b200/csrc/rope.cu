@@ -313,13 +313,14 @@ rope_halves_kernel(float* rows, int ld, int q_off, int k_off, int n_head, int di
     cs[i] = (float)cd;
     sn[i] = (float)sd;
   }
+  __syncthreads();
+  pdl_wait();
+  // (nothing is written ahead of the wait: a kernel further back may still be reading coef, which layers share)
   if (coef != nullptr)
     for (int h = threadIdx.x; h < n_head; h += blockDim.x) {
       coef[((size_t)t * n_head + h) * 2] = decay[h];
       coef[((size_t)t * n_head + h) * 2 + 1] = 1.0f;
     }
-  __syncthreads();
-  pdl_wait();
   float* p = rows + (size_t)t * ld;
   const int units = dim - half;            // per head: `half` pairs, then the values behind rot_dims
   for (int idx = threadIdx.x; idx < 2 * n_head * units; idx += blockDim.x) {

@@ -909,13 +909,12 @@ def attention(q: torch.Tensor, cache: torch.Tensor, out: torch.Tensor, block_tab
         if traced:
             _note_attention(plan.n_prefill_rows, plan.prefill_keys, plan.prefill_kv_rows, n_head, n_kv_head, head_dim,
                             q.element_size())
-        tiled = extras is None or (extras.span <= 0 and extras.head_scale is None and extras.sinks is None)
-        if tiled and q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
+        if q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_tc_supported", head_dim, page_size) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0 and out.stride(0) % 8 == 0 \
                 and out.data_ptr() % 16 == 0:
             attention_prefill_tc(q, cache, out, block_table, plan.wide_tiles, plan.n_wide_tiles, ctx.entry_start,
                                  ctx.entry_pos0, ctx.n_rows, n_head, scale, window, ctx.status, sink=sink, extras=extras)
-        elif tiled and q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
+        elif q.dtype == torch.bfloat16 and scale > 0 and _can("nib_attention_prefill_supported", head_dim) \
                 and q.stride(0) % 8 == 0 and q.data_ptr() % 16 == 0:
             attention_prefill(q, cache, out, block_table, plan.tiles, plan.n_tiles, ctx.entry_start, ctx.entry_pos0,
                               n_head, scale, window, ctx.status, sink=sink, extras=extras)
@@ -1523,10 +1522,12 @@ def short_conv(proj: torch.Tensor, c_off: int, channels: int, taps: int, w: torc
     entry's rows.  A step in which every entry is one row does both in one launch.  ``out16`` (bfloat16, optional)
     receives the same values once more, for a matrix product that reads them."""
     _f32(proj, "short_conv: proj"); _f32(out, "short_conv: out"); _f32(w, "short_conv: w")
-    if state.dtype != torch.float32:       # (a view of some columns of the slots' rows will do)
+    if state is None and taps > 1:
+        raise KernelError("short_conv: more than one tap needs the requests' state")
+    if state is not None and state.dtype != torch.float32:       # (a view of some columns of the slots' rows will do)
         raise KernelError("short_conv: state must be float32")
     if w.shape != (channels, taps) or not w.is_contiguous() or proj.stride(1) != 1 or out.stride(1) != 1 \
-            or state.stride(1) != 1 or out.shape[1] < channels:
+            or (state is not None and state.stride(1) != 1) or out.shape[1] < channels:
         raise KernelError("short_conv: w contiguous [channels, taps], rows of proj, out and state contiguous")
     T, E = ctx.n_rows, ctx.n_entries
     if out16 is not None and (out16.dtype != torch.bfloat16 or out16.stride(1) != 1 or out16.shape[1] < channels):
@@ -1535,7 +1536,8 @@ def short_conv(proj: torch.Tensor, c_off: int, channels: int, taps: int, w: torc
     if tracing():
         _note("other", "short_conv", (T, channels, taps), 2.0 * T * channels * taps, 8.0 * T * channels)
     _check(library().nib_short_conv(_ptr(proj), proj.stride(0), int(c_off), int(channels), int(taps), _ptr(w),
-                                    _ptr(bias), _ptr(state), state.stride(0), _ptr(ctx.row_entry), _ptr(ctx.entry_start),
+                                    _ptr(bias), _ptr(state), state.stride(0) if state is not None else 0, _ptr(ctx.row_entry),
+                                    _ptr(ctx.entry_start),
                                     _ptr(ctx.entry_slot), _ptr(out), out.stride(0), T, E, int(act), fused, _ptr(out16),
                                     out16.stride(0) if out16 is not None else 0, _stream()),
            "short_conv", 1 if fused or taps <= 1 else 2)

@@ -91,7 +91,7 @@ def chunked_sink_attention(h: torch.Tensor, w: Tensors, p: str, m: dict, eps: fl
 
 def retention(h: torch.Tensor, w: Tensors, p: str, m: dict, eps: float) -> torch.Tensor:
     """Linear attention with one fixed decay per head: S <- decay S + k v^T, o = S^T q; no softmax."""
-    n, H, d, dv = h.shape[0], m["heads"], m["dim"], m["vdim"]
+    n, H, d, dv = h.shape[0], m["heads"], m["dim"], m.get("vdim") or m["dim"]
     pos = torch.arange(n)
     rot = m.get("rot") or {}
     q = rotate_halves((h @ w[p + "q"].T).view(n, H, d), pos, rot.get("dims", 0), rot.get("base", 1.0))
@@ -185,7 +185,7 @@ def forward(cfg: dict, w: Tensors, tokens: Sequence[int], layers_out: Optional[l
         if layers_out is not None:
             layers_out.append(sum(X))
     x = rms(sum(X), eps) * w["final.norm"]
-    return (x @ w["head"].T) * cfg["logit_scale"]
+    return (x @ w["head"].T) * cfg.get("logit_scale", 1.0)
 
 
 def load_folder(model_dir: str):
@@ -199,3 +199,21 @@ def load_folder(model_dir: str):
         for name in f.keys():
             w[name] = f.get_tensor(name)
     return cfg, w
+
+
+class PlainNagilix:
+    """The plain model of a folder: ``logits(tokens)`` float64 [n, vocab] of a whole sequence."""
+
+    def __init__(self, model_dir: str):
+        self.cfg, self.w = load_folder(model_dir)
+
+    def logits(self, tokens: Sequence[int], layers_out: Optional[list] = None) -> torch.Tensor:
+        return forward(self.cfg, self.w, tokens, layers_out)
+
+    def greedy(self, prompt: Sequence[int], n: int) -> List[int]:
+        """The ``n`` tokens that greedy decoding appends to ``prompt`` (ties to the lower index)."""
+        seq, out = list(prompt), []
+        for _ in range(n):
+            out.append(int(torch.argmax(self.logits(seq)[-1])))
+            seq.append(out[-1])
+        return out

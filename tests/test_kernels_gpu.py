@@ -293,7 +293,7 @@ def test_both_decode_attention_kernels_at_every_split(dtype, case):
                     table.data_ptr(), table.shape[1], None, ctx.row_entry.data_ptr(), ctx.positions.data_ptr(), n_rows,
                     n_head, n_kv_head, hd, ps, cache.shape[0], scale, window, 0, chunk, n_splits, counters.data_ptr(),
                     ctx.status.data_ptr())
-            plain = (0.0, 0, None, None, 0, 1.0)     # no options on the scores or the output
+            plain = o.AttnExtras().args()           # no options on the scores or the output
             code = lib.nib_attention_decode(dt, *args[:-4], *plain, *args[-4:], stream) if kernel == "streaming" else \
                 lib.nib_attention_decode_mma(*args, int("cluster" in kernel),
                                              int(kernel.split("ring ")[1][0]) if "ring" in kernel else 0, stream)

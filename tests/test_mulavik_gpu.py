@@ -232,7 +232,7 @@ def test_every_attention_kernel_with_the_sink(hd, n_head, n_kv_head, dtype):
                     table_d.data_ptr(), table_d.shape[1], None, ctx.row_entry.data_ptr(), ctx.positions.data_ptr(), 3,
                     n_head, n_kv_head, hd, page, cache_d.shape[0], scale, 0, 1, chunk, n_splits, counters.data_ptr(),
                     ctx.status.data_ptr())
-            plain = (0.0, 0, None, None, 0, 1.0)     # no options on the scores or the output
+            plain = ops.AttnExtras().args()         # no options on the scores or the output
             code = lib.nib_attention_decode(0 if dtype == "float32" else 1, *args[:-4], *plain, *args[-4:], stream) \
                 if kernel == "streaming" else \
                 lib.nib_attention_decode_mma(*args, int("cluster" in kernel), 0, stream)
