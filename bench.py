@@ -3,7 +3,7 @@
 weights, bfloat16) at batch 8 on one B200, with prefill, roofline and end-to-end figures.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference] [--preset NAME]
-    python bench.py --compare-designs [--designs kemuzen,mulavik,vadonex,gpt2] [--widths 768,1024,1600] [--layers 4]
+    python bench.py --compare-designs [--designs nagilix,kemuzen,mulavik,vadonex,gpt2] [--widths 768,1024,1600] [--layers 4]
 
 With --compare-designs another line is printed instead: Vadonex (latent attention, delta rule, routed
 experts) beside GPT-2 at equal width, depth, vocabulary and context, prefill and decode throughput and each
@@ -64,7 +64,7 @@ def main() -> int:
                     help="Vadonex beside GPT-2 at equal layer sizes instead of the headline workload")
     ap.add_argument("--widths", default="768,1024,1600", help="with --compare-designs: the model widths")
     ap.add_argument("--designs", default="vadonex,gpt2",
-                    help="with --compare-designs: which of kemuzen, mulavik, vadonex, gpt2 stand side by side")
+                    help="with --compare-designs: which of nagilix, kemuzen, mulavik, vadonex, gpt2 stand side by side")
     ap.add_argument("--preheat", type=float, default=1.5,
                     help="seconds of untimed prefill steps before the timed loops (0: none)")
     args = ap.parse_args()

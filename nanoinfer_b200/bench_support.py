@@ -477,6 +477,32 @@ def kemuzen_like(width: int, n_layer: int, vocab: int, window: int = 512) -> dic
                 norm=dict(eps=1e-6), logit_softcap=30.0, token_side=dict(dim=32), layers=layers)
 
 
+def nagilix_like(width: int, n_layer: int, vocab: int, context: int, span: int = 512) -> dict:
+    """A Nagilix configuration whose layers have the sizes of a GPT-2 of ``width``: by turns a selective-scan layer
+    (inner 2 x width, a state of 16, step sizes of rank width / 16, four taps) and a layer with attention inside spans
+    of ``span`` positions (heads of 64, a key/value head for about four query heads, four taps, all of a head turned)
+    beside retention (half as many heads of 64 by 128, decays 1 - 2^-(5 + h)); every layer with eight routed experts
+    of width x width of which a row visits two, one more router output handing its input on; two copies of the
+    stream, a gate on every sublayer's result."""
+    heads = width // 64
+    kv_heads = max(d for d in range(1, max(1, heads // 4) + 1) if heads % d == 0)
+    r_heads = max(1, heads // 2)
+    left = dict(heads=heads, kv_heads=kv_heads, dim=64, vdim=64, scale=0.125, conv=4, mask=dict(size=span),
+                rot=dict(dims=64, base=10000.0))
+    right = dict(heads=r_heads, dim=64, vdim=128, decay=[1.0 - 2.0 ** -(5 + h % 6) for h in range(r_heads)],
+                 rot=dict(dims=64, base=10000.0))
+    scan = dict(inner=2 * width, state=16, dt_rank=max(8, width // 16), conv=4)
+    moe = dict(kind="moe", expert=dict(ff=width, limit=7.0), router=dict(experts=8, identity=1, top=2))
+    layers = []
+    for i in range(n_layer):
+        if i % 2 == 0:
+            layers.append(dict(type="mamba1", mixer=dict(scan), mlp=json.loads(json.dumps(moe))))
+        else:
+            layers.append(dict(type="parallel", mixer=dict(left=dict(left), right=dict(right)), mlp=json.loads(json.dumps(moe))))
+    return dict(architecture="Nagilix", vocab=vocab, width=width, max_positions=context, streams=2, norm=dict(eps=1e-6),
+                logit_scale=1.0, layers=layers)
+
+
 def folder_of(raw: dict, seed: int, dtype: torch.dtype) -> str:
     """A folder with seeded random weights of the configuration ``raw`` (made once, in the temporary folder)."""
     from .config.base import architecture_name
@@ -532,7 +558,7 @@ def profile_forward(eng, prompt, batch: int, repeats: int = 3):
 
 def compare_designs(widths=(768, 1024, 1600), n_layer: int = 4, batch: int = 8, context: int = 1024,
                     steps: int = 64, warmup: int = 8, designs=("vadonex", "gpt2")) -> List[dict]:
-    """The ``designs`` (of "kemuzen", "mulavik", "vadonex", "gpt2") side by side at equal width, depth, vocabulary and
+    """The ``designs`` (of "nagilix", "kemuzen", "mulavik", "vadonex", "gpt2") side by side at equal width, depth, vocabulary and
     context (random weights, bfloat16): one prompt of ``context - steps - warmup`` tokens in one step, decode at
     ``batch``, and where the time of each goes op by op with every op's fraction of its roofline (measured
     peaks)."""
@@ -544,7 +570,8 @@ def compare_designs(widths=(768, 1024, 1600), n_layer: int = 4, batch: int = 8, 
         record = {"width": width, "n_layer": n_layer, "batch": batch, "context": context}
         made = {"vadonex": lambda: vadonex_like(width, n_layer, 50257, context), "gpt2": lambda: gpt2,
                 "mulavik": lambda: mulavik_like(width, n_layer, 50257),
-                "kemuzen": lambda: kemuzen_like(width, n_layer, 50257)}
+                "kemuzen": lambda: kemuzen_like(width, n_layer, 50257),
+                "nagilix": lambda: nagilix_like(width, n_layer, 50257, context)}
         for name in designs:
             raw = made[name]()
             d = folder_of(raw, 1234, torch.bfloat16)

@@ -236,7 +236,7 @@ def main(argv=None) -> int:
 
     r = sub.add_parser("random-weights", help="write a model folder with seeded random weights")
     r.add_argument("--config", required=True, help="a preset name (gpt2-small, gpt2-medium, gpt2-xl, "
-                                                   "gpt2-tiny-a, gpt2-tiny-b, vadonex-tiny, mulavik-tiny, kemuzen-tiny) or a config.json file")
+                                                   "gpt2-tiny-a, gpt2-tiny-b, vadonex-tiny, mulavik-tiny, kemuzen-tiny, nagilix-tiny) or a config.json file")
     r.add_argument("--seed", type=int, default=0)
     r.add_argument("--out", required=True)
     r.add_argument("--dtype", default="bfloat16", choices=["bfloat16", "float32"])

@@ -1701,17 +1701,18 @@ def hyper_update(streams: torch.Tensor, y: torch.Tensor, gate: Optional[torch.Te
 
 
 # ----------------------------------------------------------------------------- the selective scan
-SSM_MAX_PER_LANE = 8
-
-
 def selective_scan_padded(n: int) -> int:
-    """The state size ``n`` rounded up to the lanes that share a channel (0: too large)."""
-    if n <= 0 or n > 32 * SSM_MAX_PER_LANE:
+    """The state size ``n`` rounded up to lanes x states a lane of the kernel (0: too large): two states a lane while
+    the lanes of a warp suffice, then 4 or 8."""
+    if n <= 0 or n > 256:
         return 0
     lanes = 1
-    while -(-n // lanes) > SSM_MAX_PER_LANE:
+    while lanes < 32 and -(-n // lanes) > 2:
         lanes *= 2
-    return -(-n // lanes) * lanes
+    per = 1
+    while per * lanes < n:
+        per *= 2
+    return lanes * per
 
 
 def selective_scan(dtp: torch.Tensor, x: torch.Tensor, bc: torch.Tensor, b_off: int, c_off: int, z: torch.Tensor,
