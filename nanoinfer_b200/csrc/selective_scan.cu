@@ -14,10 +14,12 @@
 //
 // State per request: [inner][NP] floats with NP = L * PER; the entries behind N stay zero.
 //
-// Between steps S is 32-bit.  Within a step the multiply-adds into S and the read-out's sum run in double precision,
-// and the decay enters as exp(dt A) - 1 (expm1f): a channel that forgets slowly has a decay next to 1, whose 32-bit
-// value carries the little that is forgotten with three or four digits only, the same way at every row, and over a
-// prompt of a thousand rows that error in what is remembered of the first rows grows with the distance.
+// The decay enters as exp(dt A) - 1 (expm1f) and the update is S <- S + (decay - 1) S + input: a channel that
+// forgets slowly has a decay next to 1, whose 32-bit value carries the little that is forgotten with three or four
+// digits only, the same way at every row, and over a prompt of a thousand rows that error in what is remembered of
+// the first rows grows with the distance (measured: the 32-bit model's error against a float64 one grew in
+// proportion to the position with exp(dt A) and stays flat with this form; carrying S in double precision on top
+// changes nothing more).
 #include "api.h"
 #include "common.cuh"
 
@@ -60,15 +62,14 @@ selective_scan_kernel(const float* dtp, int ld_dt, const float* x, int ldx, cons
   const int c = blockIdx.x * CH + cl;
   const bool has = c < inner;
   const int r0 = entry_start[e], n_rows = entry_start[e + 1] - r0;
-  float a[PER];
-  double S[PER];   // (within a step S is carried in double precision: see the head of the file)
+  float a[PER], S[PER];
   float* sp = state + (size_t)entry_slot[e] * state_stride + s_off + (size_t)(has ? c : 0) * NP;
 #pragma unroll
   for (int k = 0; k < PER; ++k) {
     const int n = j + k * L;
     a[k] = (has && n < N) ? -expf(A_log[(size_t)c * N + n]) : 0.0f;
     // the state belongs to this kernel alone: what it holds was written a step ago
-    S[k] = has ? (double)sp[n] : 0.0;
+    S[k] = has ? sp[n] : 0.0f;
   }
   const float d_skip = has ? D[c] : 0.0f;
   for (int i = tid; i < 2 * BUF; i += SSM_THREADS) sm[i] = 0.0f;   // (the tails behind N and the inner width stay zero)
@@ -116,8 +117,7 @@ selective_scan_kernel(const float* dtp, int ld_dt, const float* x, int ldx, cons
     for (int i = tid; i < rows * CH; i += SSM_THREADS) sdt[i] = ssm_softplus(sdt[i]);   // each step size once
     __syncthreads();
     // (lanes of channels beyond the inner width walk along with zeros: the shuffles below want whole warps)
-    float da[SSM_ROWS][PER], db[SSM_ROWS][PER];
-    double acc[SSM_ROWS];
+    float da[SSM_ROWS][PER], db[SSM_ROWS][PER], acc[SSM_ROWS];
 #pragma unroll
     for (int rr = 0; rr < SSM_ROWS; ++rr) {
       const float dt = rr < rows ? sdt[rr * CH + cl] : 0.0f;
@@ -130,30 +130,30 @@ selective_scan_kernel(const float* dtp, int ld_dt, const float* x, int ldx, cons
     }
 #pragma unroll
     for (int rr = 0; rr < SSM_ROWS; ++rr) {
-      double t = 0.0;
+      float t = 0.0f;
       if (rr < rows) {
 #pragma unroll
         for (int k = 0; k < PER; ++k) {
-          S[k] = fma((double)da[rr][k], S[k], S[k]) + (double)db[rr][k];
-          t = fma(S[k], (double)sC[rr * NP + j + k * L], t);
+          S[k] = fmaf(da[rr][k], S[k], S[k]) + db[rr][k];     // S + (decay - 1) S + input
+          t = fmaf(S[k], sC[rr * NP + j + k * L], t);
         }
       }
       acc[rr] = t;
     }
 #pragma unroll
     for (int rr = 0; rr < SSM_ROWS; ++rr) {
-      double t = acc[rr];
+      float t = acc[rr];
       for (int o = 1; o < L; o <<= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
       if (rr < rows && j == 0 && has) {
         const float xv = sx[rr * CH + cl], zv = sz[rr * CH + cl];
-        const float y = (float)fma((double)d_skip, (double)xv, t);
+        const float y = fmaf(d_skip, xv, t);
         out[(size_t)(r0 + ck * SSM_ROWS + rr) * ldo + c] = from_float<OutT>(y * (zv / (1.0f + expf(-zv))));
       }
     }
   }
   if (has) {
 #pragma unroll
-    for (int k = 0; k < PER; ++k) sp[j + k * L] = (float)S[k];
+    for (int k = 0; k < PER; ++k) sp[j + k * L] = S[k];
   }
 }
 
