@@ -481,7 +481,7 @@ def nagilix_like(width: int, n_layer: int, vocab: int, context: int, span: int =
     """A Nagilix configuration whose layers have the sizes of a GPT-2 of ``width``: by turns a selective-scan layer
     (inner 2 x width, a state of 16, step sizes of rank width / 16, four taps) and a layer with attention inside spans
     of ``span`` positions (heads of 64, a key/value head for about four query heads, four taps, all of a head turned)
-    beside retention (half as many heads of 64 by 128, decays 1 - 2^-(5 + h)); every layer with eight routed experts
+    beside retention (half as many heads of 64 by 128, decays 1 - 0.1 x 0.6^h); every layer with eight routed experts
     of width x width of which a row visits two, one more router output handing its input on; two copies of the
     stream, a gate on every sublayer's result."""
     heads = width // 64
@@ -489,7 +489,7 @@ def nagilix_like(width: int, n_layer: int, vocab: int, context: int, span: int =
     r_heads = max(1, heads // 2)
     left = dict(heads=heads, kv_heads=kv_heads, dim=64, vdim=64, scale=0.125, conv=4, mask=dict(size=span),
                 rot=dict(dims=64, base=10000.0))
-    right = dict(heads=r_heads, dim=64, vdim=128, decay=[1.0 - 2.0 ** -(5 + h % 6) for h in range(r_heads)],
+    right = dict(heads=r_heads, dim=64, vdim=128, decay=[1.0 - 0.1 * 0.6 ** (h % 8) for h in range(r_heads)],
                  rot=dict(dims=64, base=10000.0))
     scan = dict(inner=2 * width, state=16, dt_rank=max(8, width // 16), conv=4)
     moe = dict(kind="moe", expert=dict(ff=width, limit=7.0), router=dict(experts=8, identity=1, top=2))
