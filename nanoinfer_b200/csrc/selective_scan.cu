@@ -8,13 +8,13 @@
 // of them keeps the states n = j, j + L, ... (PER of them: 1, 2, 4 or 8) and A's values for them in registers, and the
 // read-out's sum over n ends with log2(L) shuffles.  A block of 128 threads owns 128 / L channels of one batch entry
 // and walks the entry's rows in order, SSM_ROWS rows at a time through a double buffer in shared memory filled by
-// cp.async: the rows' B and C, and for the block's channels dtp (turned into softplus(dtp) once it has landed), x
-// and z.  Of a chunk's rows the decays (less one) and the inputs dt x B are made first, side by side; only the
+// cp.async: the rows' B and C, and for the block's channels dtp and z (turned into softplus(dtp) and silu(z) once
+// they have landed) and x.  Of a chunk's rows the decays (less one) and the inputs dt x B are made first, side by side; only the
 // multiply-adds into S form a chain from row to row, and the read-outs' sums are taken off it afterwards.
 //
 // State per request: [inner][NP] floats with NP = L * PER; the entries behind N stay zero.
 //
-// The decay enters as exp(dt A) - 1 (expm1f) and the update is S <- S + (decay - 1) S + input: a channel that
+// The decay enters as exp(dt A) - 1 (ssm_expm1 below) and the update is S <- S + (decay - 1) S + input: a channel that
 // forgets slowly has a decay next to 1, whose 32-bit value carries the little that is forgotten with three or four
 // digits only, the same way at every row, and over a prompt of a thousand rows that error in what is remembered of
 // the first rows grows with the distance (measured: the 32-bit model's error against a float64 one grew in
@@ -29,6 +29,14 @@ constexpr int SSM_THREADS = 128;
 constexpr int SSM_ROWS = 8;      // rows staged at a time
 
 __device__ __forceinline__ float ssm_softplus(float v) { return v > 20.0f ? v : log1pf(expf(v)); }
+
+// exp(z) - 1 for z <= 0.  Below 1/16 the series up to z^6 (its next term is under 2^-36 of z); from there on
+// exp(z) - 1, whose one part in 2^24 of exp(z) is then under a part in 2^20 of what is forgotten, in channels whose
+// memory is a few hundred rows at most.
+__device__ __forceinline__ float ssm_expm1(float z) {
+  const float p = z * fmaf(z, fmaf(z, fmaf(z, fmaf(z, fmaf(z, 1.0f / 720.0f, 1.0f / 120.0f), 1.0f / 24.0f), 1.0f / 6.0f), 0.5f), 1.0f);
+  return fabsf(z) < 0.0625f ? p : expf(z) - 1.0f;
+}
 
 __device__ __forceinline__ void ssm_cp4(void* smem_dst, const void* gmem_src) {
   const uint32_t d = (uint32_t)__cvta_generic_to_shared(smem_dst);
@@ -113,8 +121,12 @@ selective_scan_kernel(const float* dtp, int ld_dt, const float* x, int ldx, cons
     float* sC = sB + SSM_ROWS * NP;
     float* sdt = sC + SSM_ROWS * NP;
     const float* sx = sdt + SSM_ROWS * CH;
-    const float* sz = sx + SSM_ROWS * CH;
-    for (int i = tid; i < rows * CH; i += SSM_THREADS) sdt[i] = ssm_softplus(sdt[i]);   // each step size once
+    float* sz = sdt + 2 * SSM_ROWS * CH;
+    for (int i = tid; i < rows * CH; i += SSM_THREADS) {   // each step size and each gate once
+      sdt[i] = ssm_softplus(sdt[i]);
+      const float zv = sz[i];
+      sz[i] = zv / (1.0f + expf(-zv));
+    }
     __syncthreads();
     // (lanes of channels beyond the inner width walk along with zeros: the shuffles below want whole warps)
     float da[SSM_ROWS][PER], db[SSM_ROWS][PER], acc[SSM_ROWS];
@@ -124,7 +136,7 @@ selective_scan_kernel(const float* dtp, int ld_dt, const float* x, int ldx, cons
       const float dx = rr < rows ? dt * sx[rr * CH + cl] : 0.0f;
 #pragma unroll
       for (int k = 0; k < PER; ++k) {
-        da[rr][k] = expm1f(dt * a[k]);   // the decay less one: what a slow channel forgets is all of its decay's information
+        da[rr][k] = ssm_expm1(dt * a[k]);   // the decay less one: what a slow channel forgets is all of its decay's information
         db[rr][k] = dx * sB[rr * NP + j + k * L];
       }
     }
@@ -145,9 +157,8 @@ selective_scan_kernel(const float* dtp, int ld_dt, const float* x, int ldx, cons
       float t = acc[rr];
       for (int o = 1; o < L; o <<= 1) t += __shfl_xor_sync(0xffffffffu, t, o);
       if (rr < rows && j == 0 && has) {
-        const float xv = sx[rr * CH + cl], zv = sz[rr * CH + cl];
-        const float y = fmaf(d_skip, xv, t);
-        out[(size_t)(r0 + ck * SSM_ROWS + rr) * ldo + c] = from_float<OutT>(y * (zv / (1.0f + expf(-zv))));
+        const float y = fmaf(d_skip, sx[rr * CH + cl], t);
+        out[(size_t)(r0 + ck * SSM_ROWS + rr) * ldo + c] = from_float<OutT>(y * sz[rr * CH + cl]);
       }
     }
   }
